@@ -1,0 +1,60 @@
+// Shared declarations of the sblocal_b200 library: the internal view of a
+// problem, the workspace layout, and the launch functions each kernel file
+// exports to the C-ABI layer (sbl_api.cu).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sblocal_b200.h"
+
+namespace sbl {
+
+// Workspace sections (byte offsets from the 256-byte aligned base).  The
+// generic path keeps phi(Q) and phi(K) in fp32; the tensor path keeps phi(K)
+// in bf16 and never materialises phi(Q).
+struct Workspace {
+  size_t wt;        // scaled projection sqrt(tau)*W: fp32 (r,E) [generic] / bf16 (r,E) [tensor]
+  size_t phik;      // (B,H,S,m)
+  size_t phiq;      // (B,H,T,m) fp32, generic path only
+  size_t qls;       // (B,H,T) fp32 query log-scales, generic path only
+  size_t beta;      // (B,H) fp32
+  size_t kv;        // (B,H,m,D) fp32
+  size_t ksum;      // (B,H,m) fp32
+  size_t partial;   // split-S partial summaries
+  size_t status;    // int32[4] device status words
+  size_t total;
+  int nsplit;       // number of S splits of the summary GEMM
+  int split_rows;   // key rows per split
+  bool tensor;      // true: tcgen05/TMA bf16 kernels are used
+};
+
+// Fills the layout for a problem; returns false (with a message) when the
+// problem is malformed.
+bool plan_workspace(const SblParams& p, Workspace* ws, const char** why);
+
+inline __host__ __device__ int64_t div_up(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- generic SIMT path (any E, D, r, w; fp32 or bf16 storage, fp32 math) ----
+cudaError_t f32_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st);
+cudaError_t f32_key_logscale(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
+cudaError_t f32_key_features(const SblParams& p, const Workspace& ws, char* base, const float* beta,
+                             float* phik_out, cudaStream_t st);
+cudaError_t f32_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* phik,
+                            float* kv, float* ksum, cudaStream_t st);
+cudaError_t f32_query_features(const SblParams& p, const Workspace& ws, char* base, float* phiq_out,
+                               float* qls_out, cudaStream_t st);
+cudaError_t f32_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
+                     const float* kv, const float* ksum, cudaStream_t st);
+
+// ---- tensor-core path (bf16 storage, tcgen05 + TMA), sbl_tc.cu ----
+bool tc_supported(const SblParams& p);
+cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st);
+cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
+cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta,
+                           float* kv, float* ksum, cudaStream_t st);
+cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
+                    const float* kv, const float* ksum, cudaStream_t st);
+
+}  // namespace sbl

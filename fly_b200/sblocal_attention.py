@@ -1,0 +1,72 @@
+"""Drop-in for the reference's `SBLocalAttention`
+(src/models/attention/sblocal_attention.py:15-137): banded exact softmax
+attention plus a Performer low-rank estimate outside the band, jointly
+normalised.  Same constructor and `forward` signature; the forward runs as
+hand-written sm_100a CUDA kernels behind the C ABI of include/sblocal_b200.h.
+
+Forward only.  There is no CPU path: CPU tensors raise.  Not built (raise
+NotImplementedError): causal=True (the reference marks it unchecked, :61),
+an attn_mask that masks anything (the reference's own assert at :106 rejects
+it), dropout in training mode, need_weights.
+"""
+import torch
+import torch.nn as nn
+
+from . import ops
+from .feature_maps_sb import SBPerformerFeatures
+
+
+class _ForwardOnly(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths):
+        return ops.sblocal_forward(query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError('sblocal_b200 implements the forward pass only')
+
+
+class SBLocalAttention(nn.Module):
+    """Arguments as in the reference (sblocal_attention.py:29-31):
+    local_context, dim_heads, nb_features=None (-> int(d ln d)),
+    ortho_scaling=0, causal=False, softmax_temp=None (-> 1/sqrt(E)),
+    attention_dropout=0.0, softmax_eps=0.0, device=None, dtype=None."""
+
+    def __init__(self, local_context, dim_heads, nb_features=None, ortho_scaling=0,
+                 causal=False, softmax_temp=None, attention_dropout=0.0, softmax_eps=0.0,
+                 device=None, dtype=None):
+        factory_kwargs = {'device': device, 'dtype': dtype}
+        super().__init__()
+        self.feature_map = SBPerformerFeatures(dim_heads, nb_features, ortho_scaling=ortho_scaling,
+                                               softmax_temp=softmax_temp, eps=softmax_eps,
+                                               **factory_kwargs)
+        self.local_context = local_context
+        self.causal = causal
+        self.softmax_temp = softmax_temp
+        self.dropout = nn.Dropout(attention_dropout)
+        self.softmax_eps = softmax_eps
+
+    def forward(self, query, key, value, attn_mask=None, key_padding_mask=None, need_weights=False,
+                return_attn_unnormalized=False):
+        """query (B,T,H,E), key (B,S,H,E), value (B,S,H,D); masks are mask
+        objects (fly_b200.masking or the reference's).  Returns
+        (out (B,T,H,D), None)."""
+        if self.causal:
+            raise NotImplementedError('causal SBLocal attention is not built')
+        if need_weights or return_attn_unnormalized:
+            raise NotImplementedError('need_weights (dense T x S attention output) is not built')
+        if self.training and self.dropout.p > 0:
+            raise NotImplementedError('attention dropout in training mode is not built')
+        if attn_mask is not None and not bool(attn_mask.all_ones):
+            raise NotImplementedError('attn_mask must be None or all ones')
+        key_lengths = None
+        if key_padding_mask is not None and not bool(key_padding_mask.all_ones):
+            key_lengths = key_padding_mask.lengths
+        self.feature_map.new_feature_map(query.device)
+        W = self.feature_map.projection_matrix
+        args = (query, key, value, W, self.local_context, self.softmax_temp, self.softmax_eps, key_lengths)
+        if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
+            out = _ForwardOnly.apply(*args)
+        else:
+            out = ops.sblocal_forward(*args)
+        return out, None

@@ -1,0 +1,144 @@
+/*
+ * sblocal_b200 -- C ABI of the B200 (sm_100a) SBLocal attention forward.
+ *
+ * The reference (HazyResearch/fly) is pure Python and has no FFI of its own;
+ * each entry point below names the reference function(s) whose work it
+ * replaces (paths relative to the reference tree).  All tensors are BORROWED
+ * device pointers: the caller (PyTorch in the Python shell) owns inputs,
+ * outputs and the workspace.  Every function returns 0 on success or a
+ * negative SblStatus; sbl_last_error() then describes the failure for the
+ * calling thread.  No function takes or returns a C++ or torch type.
+ *
+ * Notation: tau = softmax_temp, r = rows of the projection W (the feature
+ * count is m = 2r, the "cosh" Performer map), w = local_context, the window
+ * of query i is keys i - w/2 ... i - w/2 + w - 1 (integer division).
+ */
+#ifndef SBLOCAL_B200_H_
+#define SBLOCAL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SBL_ABI_VERSION 1
+
+typedef enum SblStatus {
+  SBL_OK = 0,
+  SBL_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad shape/stride/alignment            */
+  SBL_ERR_UNSUPPORTED = -2,      /* valid request this build has no kernel for          */
+  SBL_ERR_WORKSPACE = -3,        /* workspace null, misaligned or too small             */
+  SBL_ERR_CUDA = -4,             /* a CUDA runtime/driver call failed                   */
+  SBL_ERR_DEVICE_STATUS = -5     /* a kernel recorded an error (e.g. a bounded wait ran out) */
+} SblStatus;
+
+typedef enum SblDType { SBL_DTYPE_F32 = 0, SBL_DTYPE_BF16 = 1 } SblDType;
+
+/*
+ * One problem description shared by all entry points.
+ *
+ * q (B,T,H,E), k (B,S,H,E), v (B,S,H,D), out (B,T,H,D): the layouts of
+ * SBLocalAttention.forward's arguments (src/models/attention/
+ * sblocal_attention.py:48-50).  The last axis is contiguous; the other three
+ * carry ELEMENT strides, so the permuted copies the reference makes
+ * (sblocal_attention.py:73-75) are never needed.
+ *
+ * Sequence sharding: T and S count the rows present in THIS call's buffers.
+ * q_pos0 / k_pos0 are the global sequence positions of row 0 of q/out and of
+ * k/v; key_lengths (or S_total when key_lengths is null) bound the valid
+ * global key positions.  sum_lo..sum_hi (buffer rows) select the keys this
+ * rank contributes to the global summary; halo rows lie outside that range.
+ * A single-GPU call uses q_pos0 = k_pos0 = 0, S_total = S, sum_lo = 0,
+ * sum_hi = S.
+ */
+typedef struct SblParams {
+  int32_t dtype;              /* SblDType of q, k, v, out                                  */
+  int32_t B, H, T, S, E, D;   /* batch, heads, query rows, key rows, qk dim, value dim      */
+  int32_t r;                  /* projection rows; features m = 2r                          */
+  int32_t w;                  /* local_context                                             */
+  float softmax_temp;         /* tau > 0                                                   */
+  float softmax_eps;          /* eps added to every feature as eps/sqrt(m)                 */
+  const void* q;  int64_t q_stride_b, q_stride_t, q_stride_h;
+  const void* k;  int64_t k_stride_b, k_stride_s, k_stride_h;
+  const void* v;  int64_t v_stride_b, v_stride_s, v_stride_h;
+  void* out;      int64_t o_stride_b, o_stride_t, o_stride_h;
+  const float* W;             /* (r,E) fp32 row-major: projection_matrix, passed unchanged */
+  const int64_t* key_lengths; /* (B,) device int64, or null = no padding                   */
+  int64_t q_pos0, k_pos0;     /* global positions of buffer row 0                          */
+  int64_t S_total;            /* global number of keys                                     */
+  int32_t sum_lo, sum_hi;     /* key buffer rows that enter this rank's summary            */
+  int32_t reserved[4];        /* must be 0                                                 */
+} SblParams;
+
+/* ABI version (SBL_ABI_VERSION of the built library). */
+int sbl_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* sbl_last_error(void);
+
+/* 1 if the library was built with the tcgen05/TMA bf16 kernels. */
+int sbl_has_tensor_path(void);
+
+/* Bytes of device workspace (256-byte aligned base) any entry point below
+ * needs for this problem.  The workspace carries phi(K) from sbl_key_summary
+ * to sbl_band_forward, so a staged call sequence must reuse one buffer. */
+int sbl_workspace_bytes(const SblParams* p, size_t* bytes);
+
+/*
+ * Whole forward on one stream; replaces SBLocalAttention.forward
+ * (sblocal_attention.py:43-137) for need_weights=False, causal=False,
+ * attn_mask=None, dropout inactive: equals sbl_key_logscale +
+ * sbl_key_summary + sbl_band_forward with the summary kept in the workspace.
+ */
+int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * Stage 1: beta[b,h] = max over the key rows sum_lo..sum_hi and all m
+ * features of (+-sqrt(tau) W k - tau|k|^2/2 - ln(m)/2): the key log-scale of
+ * softmax_kernel(is_query=False) (src/models/attention/feature_maps_sb.py:77-78).
+ * beta: (B,H) fp32 device.  Sequence-sharded callers all-reduce it with MAX.
+ */
+int sbl_key_logscale(const SblParams* p, void* workspace, size_t workspace_bytes, float* beta,
+                     void* cuda_stream);
+
+/*
+ * Stage 2: phi(K) = exp(kd - beta) + eps/sqrt(m), zero at padded keys
+ * (feature_maps_sb.py:79-81, sblocal_attention.py:83-85), kept in the
+ * workspace for every key buffer row; kv[b,h] = phi(K)^T V (m,D) and
+ * ksum[b,h] = sum_s phi(k_s) (m) over rows sum_lo..sum_hi: linear_attention
+ * and linear_attention_normalization (src/models/attention/
+ * scatterbrain_utils.py:18-20,48-49).  kv (B,H,m,D), ksum (B,H,m): fp32
+ * device.  Sequence-sharded callers all-reduce both with SUM.
+ */
+int sbl_key_summary(const SblParams* p, void* workspace, size_t workspace_bytes, const float* beta,
+                    float* kv, float* ksum, void* cuda_stream);
+
+/*
+ * Stage 3: per query block: phi(Q) (feature_maps_sb.py:70-75), banded
+ * tau QK^T and phi(Q)phi(K)^T (the two local_dot_product calls,
+ * sblocal_attention.py:90-105), the joint normaliser (:109-115), the combined
+ * weights (:119), the banded weighted average plus the low-rank term
+ * (local_weighted_average, :121-122), written to out in (B,T,H,D) layout.
+ */
+int sbl_band_forward(const SblParams* p, void* workspace, size_t workspace_bytes, const float* beta,
+                     const float* kv, const float* ksum, void* cuda_stream);
+
+/*
+ * Feature maps alone, for parity checks against
+ * SBPerformerFeatures.forward_queries / forward_keys
+ * (feature_maps_sb.py:148-156 -> softmax_kernel :51-82).
+ *   sbl_query_features: q_prime (B,H,T,m) fp32, q_log_scale (B,H,T) fp32.
+ *   sbl_key_features:   k_prime (B,H,S,m) fp32 (padding zeroed as
+ *                       sblocal_attention.py:83-85), k_log_scale (B,H) fp32.
+ */
+int sbl_query_features(const SblParams* p, void* workspace, size_t workspace_bytes, float* q_prime,
+                       float* q_log_scale, void* cuda_stream);
+int sbl_key_features(const SblParams* p, void* workspace, size_t workspace_bytes, float* k_prime,
+                     float* k_log_scale, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SBLOCAL_B200_H_ */
