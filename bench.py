@@ -1,0 +1,328 @@
+"""Benchmark of the SBLocal attention forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one forward of the attention layer over one batch of synthetic
+inputs.  Default workload: bf16, B=2, H=16, N=16384, d=64, window 256, m=256
+(the configuration the roofline target is quoted on).  With N>1 GPUs (launched
+by torch.distributed.run, one rank per GPU) every rank runs that batch on its
+own (batch x head) units -- the path has no collective -- so the global batch
+is N times larger (weak scaling).  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the reference's forward (the
+oracle port, all host threads) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (dtype, B, H, N, d, w, m, seed)
+    'sblocal_bf16_B2_H16_N16384_d64_w256_m256': ('bf16', 2, 16, 16384, 64, 256, 256, 2),
+    'sblocal_fp32_B8_H1_N3136_d64_w256_m256': ('f32', 8, 1, 3136, 64, 256, 256, 0),
+    'sblocal_bf16_B4_H12_N4096_d64_w256_m256': ('bf16', 4, 12, 4096, 64, 256, 256, 1),
+    'sblocal_bf16_B1_H8_N131072_d128_w512_m512': ('bf16', 1, 8, 131072, 128, 512, 512, 3),
+}
+DEFAULT_WORKLOAD = 'sblocal_bf16_B2_H16_N16384_d64_w256_m256'
+METRIC = 'sblocal_attn_fwd_tokens_per_s'
+
+
+def load_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as fh:
+            pk = json.load(fh)
+        return dict(hbm_gbs=pk['hbm_gbs'], bf16_tflops=pk['bf16_tflops'],
+                    bf16_tflops_sustained=pk.get('bf16_tflops_sustained'), source='measured')
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source='fallback')
+
+
+def flops_per_token_head(d, D, w, m):
+    """Algorithmic FLOPs of the whole forward per (token, head): two r x d
+    projections, phi(K)^T V, phi(Q) KV, phi(Q).sum phi(K), band QK^T, band
+    phi(Q)phi(K)^T, band A V."""
+    return 2 * (m * d + 2 * m * D + m + w * d + w * m + w * D)
+
+
+def band_flops_per_token_head(d, D, w, m):
+    """Share of the above done by the band kernel: the query projection,
+    phi(Q) KV, phi(Q).ksum and the three banded products."""
+    return 2 * (m * d // 2 + m * D + m + w * d + w * m + w * D)
+
+
+def make_inputs(spec, device, seed_offset=0):
+    dtype, B, H, N, d, w, m, seed = spec
+    g = torch.Generator(device='cpu').manual_seed(seed + 1000 * seed_offset)
+    tdt = torch.bfloat16 if dtype == 'bf16' else torch.float32
+    scale = d ** 0.25
+    mk = lambda: (torch.randn(B, N, H, d, generator=g) / scale).to(tdt)
+    q, k, v = mk(), mk(), mk()
+    torch.manual_seed(seed)
+    from fly_b200.projection_utils import gaussian_orthogonal_random_matrix
+    W = gaussian_orthogonal_random_matrix(m // 2, d)
+    return q, k, v, W
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+    FIELDS = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+              'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.FIELDS}',
+                 '--format=csv,noheader,nounits', '-lms', '100'],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=['nvidia-smi unavailable'])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for row in self.rows:
+            parts = [x.strip() for x in row.split(',')]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith('active'):
+                    reasons.add(nm)
+        sm.sort()
+        return dict(sm_mhz=(sm[len(sm) // 2] if sm else None), sm_max_mhz=smax, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def run_reference(args, spec, rank, world):
+    """CPU arm: the oracle port of the reference forward, fp32, all host
+    threads, on a bounded sample (a few (batch, head) units at full N)."""
+    if rank != 0:
+        return
+    from oracle import sblocal_oracle as so
+    dtype, B, H, N, d, w, m, seed = spec
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    units = max(1, min(B * H, args.cpu_units))
+    q, k, v, W = make_inputs((dtype, units, 1, N, d, w, m, seed), 'cpu')
+    q, k, v = q.float(), k.float(), v.float()
+    times = []
+    for i in range(args.warmup_cpu + args.steps_cpu):
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            so.sblocal_forward(q, k, v, W, w, row_chunk=1024)
+        if i >= args.warmup_cpu:
+            times.append(time.perf_counter() - t0)
+    t = sum(times) / len(times)
+    # tokens/s of the full workload = token-heads/s divided by H
+    value = units * N / t / H
+    line = dict(metric=METRIC, value=value, unit='tokens/s', impl='reference', n_gpus=args.gpus,
+                steps=args.steps_cpu, warmup=args.warmup_cpu, ms_per_step=t * 1e3, higher_is_better=True,
+                scaling='weak', vs_baseline=None, dtype='f32', data='synthetic',
+                config=dict(workload=args.workload, B=B, H=H, N=N, d=d, window=w, features=m),
+                cpu_baseline=dict(value=value, unit='tokens/s', cores=cores, kind='port',
+                                  sample=f'{units} of {B * H} (batch,head) units at full N={N}, fp32, '
+                                         f'scaled to whole-batch tokens/s'),
+                e2e=dict(value=value, unit='tokens/s', h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=50)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--workload', default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--cpu-units', type=int, default=2, help='(batch,head) units in the CPU sample')
+    ap.add_argument('--steps-cpu', type=int, default=2)
+    ap.add_argument('--warmup-cpu', type=int, default=1)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    spec = WORKLOADS[args.workload]
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+
+    if args.impl == 'reference':
+        run_reference(args, spec, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the SBLocal path has no CPU fallback')
+    import torch.distributed as dist
+    from fly_b200 import _cabi, ops
+    from fly_b200.sblocal_attention import SBLocalAttention
+    _cabi.load()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    args.warmup = max(args.warmup, 3)
+
+    dtype, B, H, N, d, w, m, seed = spec
+    q_h, k_h, v_h, W = make_inputs(spec, 'cpu', seed_offset=rank)
+    q_h, k_h, v_h = q_h.pin_memory(), k_h.pin_memory(), v_h.pin_memory()
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    Wd = W.to(dev)
+    prob = ops.Problem(q, k, v, Wd, w)
+    tensor_path = bool(_cabi.load().sbl_has_tensor_path()) and dtype == 'bf16'
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing: `value` --------------------------------
+    for _ in range(args.warmup):
+        prob.forward()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        prob.forward()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- per-stage timing on the launch stream (roofline of the band kernel) ----
+    beta = prob.key_logscale()
+    kv, ksum = prob.key_summary(beta)
+    prob.band_forward(beta, kv, ksum)
+    torch.cuda.synchronize(dev)
+    nb = max(5, min(args.steps, 20))
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nb)]
+    for a, b in evs:
+        prob.key_summary(beta)          # evicts the band kernel's inputs from L2 between repeats
+        a.record()
+        prob.band_forward(beta, kv, ksum)
+        b.record()
+    torch.cuda.synchronize(dev)
+    band_ms = sum(a.elapsed_time(b) for a, b in evs) / nb
+
+    # ---- end to end through the module: host buffers in, host buffer out ----
+    layer = SBLocalAttention(w, d, m).to(dev).eval()
+    layer.feature_map.new_feature_map(dev)
+    layer.feature_map.projection_matrix.copy_(Wd)
+    out_h = torch.empty(B, N, H, d, dtype=q_h.dtype).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        qd, kd, vd = q_h.to(dev, non_blocking=True), k_h.to(dev, non_blocking=True), v_h.to(dev, non_blocking=True)
+        with torch.no_grad():
+            o, _ = layer(qd, kd, vd)
+        out_h.copy_(o, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    e2e_ms = s0.elapsed_time(s1)
+
+    t = torch.tensor([ms, e2e_ms, band_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, band_ms = (float(x) for x in t.tolist())
+
+    if rank == 0:
+        peaks = load_peaks()
+        tokens_per_step = world * B * N
+        ms_per_step = ms / args.steps
+        value = tokens_per_step / (ms_per_step * 1e-3)
+        e2e_value = tokens_per_step / (e2e_ms / e2e_steps * 1e-3)
+        th = B * H * N
+        band_flops = band_flops_per_token_head(d, d, w, m) * th
+        fwd_flops = flops_per_token_head(d, d, w, m) * th
+        elem = 2 if dtype == 'bf16' else 4
+        peak_tf = peaks['bf16_tflops']
+        achieved = band_flops / (band_ms * 1e-3) / 1e12
+        launches_per_step = 5 if tensor_path else 8
+        line = dict(
+            metric=METRIC, value=value, unit='tokens/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
+            ms_per_step=ms_per_step, higher_is_better=True, scaling='weak', vs_baseline=None,
+            dtype='bf16' if dtype == 'bf16' else 'f32', data='synthetic',
+            config=dict(workload=args.workload, B_per_gpu=B, global_batch=world * B, H=H, N=N, d=d, window=w,
+                        features=m, sharding='batch x head, no collective',
+                        l2='inputs of one step (%.0f MB) exceed the 126 MB L2' % (4 * th * d * elem / 1e6),
+                        kernels='tcgen05+TMA bf16' if tensor_path else 'generic SIMT fp32 math'),
+            clocks=clocks,
+            e2e=dict(value=e2e_value, unit='tokens/s', h2d_bytes_per_step=3 * th * d * elem,
+                     d2h_bytes_per_step=th * d * elem, steps=e2e_steps),
+            gpu_launches=launches_per_step * args.steps,
+            roofline=dict(bound='tensor', kernel='band', achieved=achieved, peak=peak_tf, unit='TFLOP/s',
+                          frac=achieved / peak_tf, traffic=None, peak_source=peaks['source'],
+                          kernel_ms=band_ms),
+            roofline_forward=dict(bound='tensor', achieved=fwd_flops / (ms_per_step * 1e-3) / 1e12, peak=peak_tf,
+                                  unit='TFLOP/s', frac=fwd_flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
+                                  hbm_gbs=4 * th * d * elem / (ms_per_step * 1e-3) / 1e9,
+                                  hbm_peak_gbs=peaks['hbm_gbs']),
+        )
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import sblocal_oracle as so
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            units = max(1, min(B * H, args.cpu_units))
+            cq, ck, cv, cW = make_inputs((dtype, units, 1, N, d, w, m, seed), 'cpu')
+            cq, ck, cv = cq.float(), ck.float(), cv.float()
+            with torch.no_grad():
+                so.sblocal_forward(cq, ck, cv, cW, w, row_chunk=1024)
+                t0 = time.perf_counter()
+                ref_out, _ = so.sblocal_forward(cq, ck, cv, cW, w, row_chunk=1024)
+                cpu_t = time.perf_counter() - t0
+            line['cpu_baseline'] = dict(
+                value=units * N / cpu_t / H, unit='tokens/s', cores=cores, kind='port',
+                sample=f'{units} of {B * H} (batch,head) units at full N={N}, fp32, scaled to whole-batch tokens/s')
+            # the same sample through the CUDA path, as a live parity figure
+            dq, dk, dv = (x.to(dev).to(q.dtype) for x in (cq, ck, cv))
+            got = ops.sblocal_forward(dq, dk, dv, cW.to(dev), w).float().cpu()
+            line['parity_vs_cpu_sample'] = so.rel_err(got, ref_out)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()
