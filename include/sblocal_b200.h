@@ -138,6 +138,23 @@ int sbl_query_features(const SblParams* p, void* workspace, size_t workspace_byt
 int sbl_key_features(const SblParams* p, void* workspace, size_t workspace_bytes, float* k_prime,
                      float* k_log_scale, void* cuda_stream);
 
+/*
+ * No counterpart in the reference: an addition for hosts that are not allowed
+ * to allocate device memory (a process whose GPU memory is owned by one
+ * start-up arena, or a loop in which cudaMalloc is banned because it stalls
+ * the device) and so cannot supply a workspace.  Same result as
+ * sbl_key_logscale, but the scratch (sqrt(tau)*W, r*E floats) is a fixed
+ * 128 KiB array inside the library image, present on every GPU that loads the
+ * library.  Limits: r*E <= SBL_STATIC_PROJ_FLOATS, else SBL_ERR_UNSUPPORTED.
+ * All calls on a device share that array; calls that overlap on the GPU race
+ * on it, so keep them on one stream.  The first call on each device resolves
+ * the array's address through the CUDA runtime: make it at start-up, before
+ * any stream capture.  Allocates nothing.  Errors: sbl_static_last_error().
+ */
+#define SBL_STATIC_PROJ_FLOATS 32768
+int sbl_key_logscale_static(const SblParams* p, float* beta, void* cuda_stream);
+const char* sbl_static_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif
