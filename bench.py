@@ -32,6 +32,8 @@ WORKLOADS = {
     'sblocal_fp32_B8_H1_N3136_d64_w256_m256': ('f32', 8, 1, 3136, 64, 256, 256, 0),
     'sblocal_bf16_B4_H12_N4096_d64_w256_m256': ('bf16', 4, 12, 4096, 64, 256, 256, 1),
     'sblocal_bf16_B1_H8_N131072_d128_w512_m512': ('bf16', 1, 8, 131072, 128, 512, 512, 3),
+    # a quarter of the default batch: small enough for a multi-pass ncu capture
+    'sblocal_bf16_B2_H4_N16384_d64_w256_m256': ('bf16', 2, 4, 16384, 64, 256, 256, 2),
 }
 DEFAULT_WORKLOAD = 'sblocal_bf16_B2_H16_N16384_d64_w256_m256'
 METRIC = 'sblocal_attn_fwd_tokens_per_s'
@@ -172,6 +174,8 @@ def main():
     ap.add_argument('--steps-cpu', type=int, default=2)
     ap.add_argument('--warmup-cpu', type=int, default=1)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--profile', action='store_true',
+                    help='run only warm-up and the timed forwards (for ncu captures); prints no JSON line')
     args = ap.parse_args()
     spec = WORKLOADS[args.workload]
     rank = int(os.environ.get('RANK', '0'))
@@ -222,6 +226,10 @@ def main():
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
+    if args.profile:
+        prob.check_status()
+        print(f'profile run: {ms / args.steps:.4f} ms per forward (not a benchmark value)')
+        return
 
     # ---- per-stage timing on the launch stream (roofline of the band kernel) ----
     beta = prob.key_logscale()
@@ -266,6 +274,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms, band_ms = (float(x) for x in t.tolist())
+    prob.check_status()     # raises if any kernel gave up on a bounded wait
 
     if rank == 0:
         peaks = load_peaks()
@@ -279,7 +288,7 @@ def main():
         elem = 2 if dtype == 'bf16' else 4
         peak_tf = peaks['bf16_tflops']
         achieved = band_flops / (band_ms * 1e-3) / 1e12
-        launches_per_step = 5 if tensor_path else 8
+        launches_per_step = 7 if tensor_path else 8
         line = dict(
             metric=METRIC, value=value, unit='tokens/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=ms_per_step, higher_is_better=True, scaling='weak', vs_baseline=None,

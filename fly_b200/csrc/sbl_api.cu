@@ -81,7 +81,9 @@ int prepare(const SblParams* p, void* workspace, size_t bytes, Workspace* ws) {
   return check_workspace(*ws, workspace, bytes);
 }
 
-// Reads the device status words a tensor-path kernel may have set.
+// Tensor-path kernels record a ran-out wait in the workspace status word; it
+// is read (with a stream synchronisation) only by sbl_check_status, so the
+// forward itself never blocks the host.
 int check_device_status(const Workspace& ws, char* base, cudaStream_t st) {
   (void)ws; (void)base; (void)st;
   return SBL_OK;
@@ -98,11 +100,20 @@ bool plan_workspace(const SblParams& p, Workspace* ws, const char** why) {
   while (div_up(rows > 0 ? rows : 1, split_rows) > 64) split_rows *= 2;
   ws->split_rows = split_rows;
   ws->nsplit = (int)div_up(rows > 0 ? rows : 1, split_rows);
+  if (ws->tensor) {
+    // tensor path: CTAs stream 128-key tiles; about two CTAs per SM-count over all (b,h)
+    const int ntiles = (int)div_up(p.S, 128);
+    int ns = (int)((296 + BH / 2) / BH);
+    if (ns < 1) ns = 1;
+    if (ns > ntiles) ns = ntiles;
+    ws->nsplit = ns;
+    ws->split_rows = 0;
+  }
   size_t off = 0;
   ws->wt = off;      off = align_up(off + (size_t)p.r * p.E * sizeof(float));
   ws->phik = off;    off = align_up(off + BH * p.S * m * (ws->tensor ? 2 : 4));
-  ws->phiq = off;    off = align_up(off + (ws->tensor ? 0 : BH * p.T * m * 4));
-  ws->qls = off;     off = align_up(off + (ws->tensor ? 0 : BH * p.T * 4));
+  ws->phiq = off;    off = align_up(off + (ws->tensor ? (size_t)p.r * p.E * 2 : BH * p.T * m * 4));
+  ws->qls = off;     off = align_up(off + (ws->tensor ? BH * m * p.D * 2 : BH * p.T * 4));
   ws->beta = off;    off = align_up(off + BH * 4);
   ws->kv = off;      off = align_up(off + BH * m * p.D * 4);
   ws->ksum = off;    off = align_up(off + BH * m * 4);
@@ -154,7 +165,7 @@ int sbl_key_logscale(const SblParams* p, void* workspace, size_t workspace_bytes
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   cudaError_t e;
   if (ws.tensor) {
-    if ((e = tc_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
+    if ((e = tc_prepare_projection(*p, ws, base, st, true)) != cudaSuccess) return cuda_fail(e, "prepare projection");
     if ((e = tc_key_logscale(*p, ws, base, beta, st)) != cudaSuccess) return cuda_fail(e, "key logscale");
   } else {
     if ((e = f32_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
@@ -173,7 +184,7 @@ int sbl_key_summary(const SblParams* p, void* workspace, size_t workspace_bytes,
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   cudaError_t e;
   if (ws.tensor) {
-    if ((e = tc_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
+    if ((e = tc_prepare_projection(*p, ws, base, st, false)) != cudaSuccess) return cuda_fail(e, "prepare projection");
     if ((e = tc_key_summary(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "key summary");
     return check_device_status(ws, base, st);
   }
@@ -194,7 +205,7 @@ int sbl_band_forward(const SblParams* p, void* workspace, size_t workspace_bytes
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
   cudaError_t e;
   if (ws.tensor) {
-    if ((e = tc_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
+    if ((e = tc_prepare_projection(*p, ws, base, st, false)) != cudaSuccess) return cuda_fail(e, "prepare projection");
     if ((e = tc_band(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "band forward");
     return check_device_status(ws, base, st);
   }
@@ -217,7 +228,7 @@ int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, voi
   float* ksum = reinterpret_cast<float*>(base + ws.ksum);
   cudaError_t e;
   if (ws.tensor) {
-    if ((e = tc_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
+    if ((e = tc_prepare_projection(*p, ws, base, st, true)) != cudaSuccess) return cuda_fail(e, "prepare projection");
     if ((e = tc_key_logscale(*p, ws, base, beta, st)) != cudaSuccess) return cuda_fail(e, "key logscale");
     if ((e = tc_key_summary(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "key summary");
     if ((e = tc_band(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "band forward");
@@ -232,6 +243,24 @@ int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, voi
                               reinterpret_cast<float*>(base + ws.qls), st)) != cudaSuccess)
     return cuda_fail(e, "query features");
   if ((e = f32_band(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "band forward");
+  return SBL_OK;
+}
+
+int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  Workspace ws;
+  int rc = prepare(p, workspace, workspace_bytes, &ws);
+  if (rc != SBL_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  if (!ws.tensor) {
+    cudaError_t e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? SBL_OK : cuda_fail(e, "stream synchronize");
+  }
+  int host = 0;
+  cudaError_t e = tc_read_status(ws, static_cast<char*>(workspace), &host, st);
+  if (e != cudaSuccess) return cuda_fail(e, "read device status");
+  if (host != 0)
+    return fail(SBL_ERR_DEVICE_STATUS, "a bounded wait ran out inside a kernel (wait site %d); results are invalid",
+                host);
   return SBL_OK;
 }
 

@@ -17,8 +17,8 @@ namespace sbl {
 struct Workspace {
   size_t wt;        // scaled projection sqrt(tau)*W: fp32 (r,E) [generic] / bf16 (r,E) [tensor]
   size_t phik;      // (B,H,S,m)
-  size_t phiq;      // (B,H,T,m) fp32, generic path only
-  size_t qls;       // (B,H,T) fp32 query log-scales, generic path only
+  size_t phiq;      // generic: phi(Q) (B,H,T,m) fp32; tensor: scaled projection in bf16 (r,E)
+  size_t qls;       // generic: query log-scales (B,H,T) fp32; tensor: KV in bf16 (B,H,m,D)
   size_t beta;      // (B,H) fp32
   size_t kv;        // (B,H,m,D) fp32
   size_t ksum;      // (B,H,m) fp32
@@ -43,6 +43,8 @@ cudaError_t f32_key_features(const SblParams& p, const Workspace& ws, char* base
                              float* phik_out, cudaStream_t st);
 cudaError_t f32_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* phik,
                             float* kv, float* ksum, cudaStream_t st);
+cudaError_t f32_combine_partials(const SblParams& p, const Workspace& ws, char* base, float* kv, float* ksum,
+                                 cudaStream_t st);
 cudaError_t f32_query_features(const SblParams& p, const Workspace& ws, char* base, float* phiq_out,
                                float* qls_out, cudaStream_t st);
 cudaError_t f32_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
@@ -50,11 +52,15 @@ cudaError_t f32_band(const SblParams& p, const Workspace& ws, char* base, const 
 
 // ---- tensor-core path (bf16 storage, tcgen05 + TMA), sbl_tc.cu ----
 bool tc_supported(const SblParams& p);
-cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st);
+// reset_status: clear the device status words (first stage of a call sequence)
+cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
+                                  bool reset_status);
 cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
 cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta,
                            float* kv, float* ksum, cudaStream_t st);
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
                     const float* kv, const float* ksum, cudaStream_t st);
+// copies the device status word to *host_status and synchronises the stream
+cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st);
 
 }  // namespace sbl

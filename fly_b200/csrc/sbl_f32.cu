@@ -561,6 +561,13 @@ cudaError_t f32_key_summary(const SblParams& p, const Workspace& ws, char* base,
                                                                  ws.split_rows, dtiles, partial);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  return f32_combine_partials(p, ws, base, kv, ksum, st);
+}
+
+cudaError_t f32_combine_partials(const SblParams& p, const Workspace& ws, char* base, float* kv, float* ksum,
+                                 cudaStream_t st) {
+  const int m = 2 * p.r, bh = p.B * p.H;
+  const float* partial = reinterpret_cast<const float*>(base + ws.partial);
   const int64_t n = (int64_t)bh * m * (p.D + 1);
   summary_combine_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(partial, ws.nsplit, m, p.D, bh, kv, ksum);
   return cudaGetLastError();

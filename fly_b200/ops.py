@@ -103,6 +103,10 @@ class Problem:
         self._call(_cabi.load().sbl_forward, workspace=workspace)
         return self.out
 
+    def check_status(self, workspace=None):
+        """Synchronises the stream; raises if a kernel gave up on a bounded wait."""
+        self._call(_cabi.load().sbl_check_status, workspace=workspace)
+
     def key_logscale(self, workspace=None):
         B, H = self.shape[:2]
         beta = torch.empty(B, H, device=self.device, dtype=torch.float32)

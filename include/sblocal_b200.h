@@ -126,6 +126,16 @@ int sbl_band_forward(const SblParams* p, void* workspace, size_t workspace_bytes
                      const float* kv, const float* ksum, void* cuda_stream);
 
 /*
+ * Synchronises the stream and reports whether any kernel of the preceding
+ * calls on this workspace gave up on a bounded wait (every device-side wait
+ * has an iteration limit, after which the kernel records the wait site,
+ * finishes and frees its tensor memory): SBL_ERR_DEVICE_STATUS if so, and the
+ * outputs of those calls are invalid.  No counterpart in the reference (its
+ * device faults surface as CUDA errors).
+ */
+int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
  * Feature maps alone, for parity checks against
  * SBPerformerFeatures.forward_queries / forward_keys
  * (feature_maps_sb.py:148-156 -> softmax_kernel :51-82).

@@ -1,0 +1,113 @@
+"""The bf16 tensor-core kernels (E = D = 64, m = 256) against the CPU oracle
+run in fp32 on the same bf16-rounded inputs.  Bound: max|out - ref| / max|ref|
+<= 2e-2.  Every call is followed by sbl_check_status, which fails if a
+device-side bounded wait ran out."""
+import pytest
+import torch
+
+from oracle import sblocal_oracle as so
+
+pytestmark = pytest.mark.gpu
+TOL_BF16 = 2e-2
+
+
+def _inputs(B, T, S, H, seed, scale=None):
+    g = torch.Generator().manual_seed(seed)
+    E = 64
+    scale = scale or E ** 0.25
+    q = (torch.randn(B, T, H, E, generator=g) / scale).bfloat16()
+    k = (torch.randn(B, S, H, E, generator=g) / scale).bfloat16()
+    v = (torch.randn(B, S, H, E, generator=g) / scale).bfloat16()
+    torch.manual_seed(seed)
+    W = so.gaussian_orthogonal_random_matrix(128, E)
+    return q, k, v, W
+
+
+def _run(q, k, v, W, w, tau=None, lengths=None):
+    from fly_b200 import ops
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), w, tau, 0.0,
+                     lengths.cuda() if lengths is not None else None)
+    out = pr.forward()
+    pr.check_status()
+    return out.float().cpu()
+
+
+def test_library_reports_tensor_path(sbl_lib):
+    assert sbl_lib.sbl_has_tensor_path() == 1
+
+
+@pytest.mark.parametrize('T,S,w', [(640, 640, 256), (1000, 1000, 256), (130, 130, 256), (777, 777, 33),
+                                   (512, 512, 100), (300, 300, 257), (64, 64, 8), (500, 380, 128),
+                                   (380, 500, 128), (1, 1, 4)])
+def test_shapes(T, S, w, sbl_lib):
+    q, k, v, W = _inputs(2, T, S, 2, seed=T + S + w)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
+    out = _run(q, k, v, W, w)
+    assert torch.isfinite(out).all()
+    assert so.rel_err(out, ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize('tau', [147 ** -0.5, 576 ** -0.5, 0.3])
+def test_temperatures(tau, sbl_lib):
+    q, k, v, W = _inputs(1, 700, 700, 3, seed=5)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 256, tau)
+    assert so.rel_err(_run(q, k, v, W, 256, tau), ref) <= TOL_BF16
+
+
+def test_ragged_lengths(sbl_lib):
+    q, k, v, W = _inputs(4, 600, 600, 2, seed=9)
+    lengths = torch.tensor([600, 150, 411, 1])
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 256, None, 0.0, lengths)
+    assert so.rel_err(_run(q, k, v, W, 256, None, lengths), ref) <= TOL_BF16
+
+
+def test_unit_variance_inputs(sbl_lib):
+    """N(0,1) inputs (the reference test's scale): larger logits, wider
+    dynamic range of the features."""
+    q, k, v, W = _inputs(2, 400, 400, 2, seed=13, scale=1.0)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 64)
+    assert so.rel_err(_run(q, k, v, W, 64), ref) <= TOL_BF16
+
+
+def test_summary_matches_oracle(sbl_lib):
+    from fly_b200 import ops
+    q, k, v, W = _inputs(2, 900, 900, 2, seed=21)
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), 256)
+    beta = pr.key_logscale()
+    kv, ksum = pr.key_summary(beta)
+    pr.check_status()
+    kp, beta_ref = so.key_features(k.float().permute(0, 2, 1, 3), W, 64 ** -0.5)
+    # the library's beta comes from the bf16-rounded projection; any beta is a valid stabiliser
+    assert torch.allclose(beta.cpu(), beta_ref.reshape(beta.shape), atol=5e-2)
+    scale = torch.exp(beta_ref.reshape(2, 2) - beta.cpu())
+    kv_ref = torch.einsum('bhsm,bhsd->bhmd', kp, v.float().permute(0, 2, 1, 3)) * scale[..., None, None]
+    assert so.rel_err(kv.cpu(), kv_ref) < 1e-2
+    assert so.rel_err(ksum.cpu(), kp.sum(-2) * scale[..., None]) < 1e-2
+
+
+@pytest.mark.parametrize('chunks', [2, 3])
+def test_sequence_shards_on_one_gpu(chunks, sbl_lib):
+    from fly_b200 import ops
+    q, k, v, W = _inputs(1, 1200, 1200, 2, seed=31)
+    w = 256
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
+    q, k, v, W = q.cuda(), k.cuda(), v.cuda(), W.cuda()
+    N = 1200
+    bounds = [N * i // chunks // 8 * 8 for i in range(chunks)] + [N]
+    probs = []
+    for g in range(chunks):
+        lo, hi = bounds[g], bounds[g + 1]
+        klo, khi = max(0, lo - w // 2), min(N, hi - 1 - w // 2 + w)
+        out = torch.empty(1, hi - lo, 2, 64, device='cuda', dtype=torch.bfloat16)
+        probs.append(ops.Problem(q[:, lo:hi], k[:, klo:khi], v[:, klo:khi], W, w, None, 0.0, None, out,
+                                 q_pos0=lo, k_pos0=klo, S_total=N, sum_range=(lo - klo, hi - klo)))
+    ws = [torch.empty(p.workspace_bytes, dtype=torch.uint8, device='cuda') for p in probs]
+    beta = torch.stack([p.key_logscale(workspace=x) for p, x in zip(probs, ws)]).amax(0)
+    parts = [p.key_summary(beta, workspace=x) for p, x in zip(probs, ws)]
+    kv = torch.stack([a for a, _ in parts]).sum(0)
+    ksum = torch.stack([b for _, b in parts]).sum(0)
+    outs = [p.band_forward(beta, kv, ksum, workspace=x) for p, x in zip(probs, ws)]
+    for p, x in zip(probs, ws):
+        p.check_status(workspace=x)
+    out = torch.cat(outs, dim=1).float().cpu()
+    assert so.rel_err(out, ref) <= TOL_BF16
