@@ -66,7 +66,8 @@ _lib = None
 
 
 def library_path():
-    return _build.LIB_PATH
+    """In-tree library, or the file named by SBLOCAL_B200_LIB (debug builds)."""
+    return os.environ.get('SBLOCAL_B200_LIB') or _build.LIB_PATH
 
 
 def load():

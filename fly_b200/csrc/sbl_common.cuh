@@ -23,7 +23,7 @@ struct Workspace {
   size_t kv;        // (B,H,m,D) fp32
   size_t ksum;      // (B,H,m) fp32
   size_t partial;   // split-S partial summaries
-  size_t status;    // int32[4] device status words
+  size_t status;    // int32[4] device status words, then small scalars
   size_t total;
   int nsplit;       // number of S splits of the summary GEMM
   int split_rows;   // key rows per split

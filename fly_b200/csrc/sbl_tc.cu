@@ -16,12 +16,12 @@
 //             tensor memory (the A operand of every phi(Q) product); then per
 //             64-key tile S = Q K^T, P = phi(Q) phi(K)^T (double-buffered in
 //             tensor memory), the softmax warps form
-//             D = exp(tau S - c) - P e^{pls-c} (masked to the window and key
-//             length) as packed bf16 in tensor memory, O += D V; finally
-//             LR = phi(Q) KV and out = (O + e^{pls-c} LR) /
-//             (L + max(Z - dps, 1e-24) e^{pls-c}), written as 128-byte rows.
-//   The row stabiliser c is the Cauchy-Schwarz bound tau |q| max|k| over the
-//   keys the CTA visits, so no accumulator is ever rescaled.
+//             D = exp(tau S - pls) - P (masked to the window and key length) as
+//             packed bf16 in tensor memory, O = phi(Q) KV + sum D V; finally
+//             out = O / (L + max(Z - dps, 1e-24)), written as 128-byte rows.
+//   Everything is kept in "feature units" (divided by e^{pls}, pls = query
+//   log-scale + beta), so the exact and the low-rank terms share one
+//   accumulator and no accumulator is ever rescaled.
 #include "sbl_common.cuh"
 #include "sbl_tc_ptx.cuh"
 
@@ -66,15 +66,36 @@ __device__ __forceinline__ float row_sumsq_sw128(const uint8_t* tile, int row) {
 }
 
 // ---------------------------------------------------------------------------
-__global__ void tc_prep_kernel(const float* W, float c, float* wt32, __nv_bfloat16* wt16, int n, int* status,
-                               int reset_status) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) {
+// One block: sqrt(tau)*W in fp32 and bf16, the largest row norm of the bf16
+// copy (bound on |u_f| / |x| used as the query feature stabiliser), status reset.
+__global__ void __launch_bounds__(256) tc_prep_kernel(const float* W, float c, float* wt32, __nv_bfloat16* wt16, int r,
+                                                      int E, int* status, float* wmax, int reset_status) {
+  __shared__ float red[8];
+  const int n = r * E;
+  for (int i = threadIdx.x; i < n; i += 256) {
     const float v = c * W[i];
     wt32[i] = v;
     wt16[i] = __float2bfloat16_rn(v);
   }
-  if (reset_status && i < 4) status[i] = 0;
+  __syncthreads();
+  float mx = 0.f;
+  for (int f = threadIdx.x; f < r; f += 256) {
+    float s = 0.f;
+    for (int e = 0; e < E; ++e) {
+      const float v = __bfloat162float(wt16[f * E + e]);
+      s = fmaf(v, v, s);
+    }
+    mx = fmaxf(mx, s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+    *wmax = sqrtf(mx) * 1.0005f;
+  }
+  if (reset_status && threadIdx.x < 4) status[threadIdx.x] = 0;
 }
 
 __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64_t n) {
@@ -85,7 +106,7 @@ __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64
 // ---------------------------------------------------------------------------
 // keys kernel
 struct KeysArgs {
-  CUtensorMap tm_k, tm_v, tm_w;
+  CUtensorMap tm_k, tm_v, tm_w, tm_phik;
   const int64_t* lengths;
   const float* beta_in;   // !MAX
   float* beta_out;        // MAX
@@ -99,35 +120,45 @@ struct KeysArgs {
 
 namespace keys {
 constexpr int TILE = 128;
+constexpr int NFEAT = 256;                 // feature threads: warps 0-7; warp w owns key rows 32*(w%4).., projection half w/4
+constexpr int NTHREADS = NFEAT + 64;       // + producer warp 8 + MMA warp 9
 constexpr uint32_t OFF_W = 0;                    // 16 KB  [128 r][64 e]
-constexpr uint32_t OFF_ONES = 16384;             // 4 KB   [128 keys][16] (32-byte swizzle)
-constexpr uint32_t OFF_STAGE = 24576;            // 2 x { K 16 KB, V 16 KB }
-constexpr uint32_t STAGE_BYTES = 32768;
-constexpr uint32_t OFF_A = OFF_STAGE + 2 * STAGE_BYTES;  // 64 KB: 4 blocks [128 keys][64 f]
+constexpr uint32_t OFF_STAGE = 16384;            // 2 x { K 16 KB, V 16 KB, ones 16 KB }: [V | 1] is one MN-major operand, N = 80
+constexpr uint32_t STAGE_BYTES = 49152;
+constexpr uint32_t OFF_A = OFF_STAGE + 2 * STAGE_BYTES;  // 64 KB: 4 blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
 constexpr uint32_t OFF_BAR = OFF_A + 65536;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;    // + alignment slack
 // tensor memory columns
 constexpr uint32_t T_UK = 0;      // 2 x 128
-constexpr uint32_t T_KV = 256;    // 2 x 64
-constexpr uint32_t T_KS = 384;    // 2 x 16
+constexpr uint32_t T_KV = 256;    // 2 x 128 (80 used): [KV (64) | sum phi(K) (16 identical columns)] for feature blocks 0-127, 128-255
 }  // namespace keys
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 template <bool MAX_ONLY>
-__global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ KeysArgs a) {
+__global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_constant__ KeysArgs a) {
   using namespace keys;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint64_t* bar_w = bars + 0;
   uint64_t* bar_done = bars + 1;
-  uint64_t* full = bars + 2;      // [2]
-  uint64_t* empty = bars + 4;     // [2]
-  uint64_t* uk_full = bars + 6;   // [2]
-  uint64_t* uk_free = bars + 8;   // [2]
-  uint64_t* a_full = bars + 10;
-  uint64_t* a_free = bars + 11;
+  uint64_t* full = bars + 2;      // [2] K (and V) tile landed
+  uint64_t* empty = bars + 4;     // [2] stage may be refilled
+  uint64_t* uk_full = bars + 6;   // [2] U = K Wt^T computed
+  uint64_t* uk_free = bars + 8;   // [2] U read by all feature threads
+  uint64_t* a_full = bars + 10;   // phi(K) tile written to shared memory
+  uint64_t* a_free = bars + 11;   // phi(K) tile consumed (MMA done + bulk store has read it)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  float* red = reinterpret_cast<float*>(bars + 13);  // [4]
+  float* red = reinterpret_cast<float*>(bars + 13);  // [8]
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
@@ -136,6 +167,7 @@ __global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ Ke
   const int t_lo = (int)((int64_t)ntiles * split / a.nsplit);
   const int t_hi = (int)((int64_t)ntiles * (split + 1) / a.nsplit);
   const int nt = t_hi - t_lo;
+  const int64_t len_b = a.lengths ? min(a.lengths[b], a.S_total) : a.S_total;
 
   if (tid == 0) {
     mbar_init(bar_w, 1);
@@ -144,36 +176,48 @@ __global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ Ke
       mbar_init(full + i, 1);
       mbar_init(empty + i, 1);
       mbar_init(uk_full + i, 1);
-      mbar_init(uk_free + i, 128);
+      mbar_init(uk_free + i, NFEAT);
     }
-    mbar_init(a_full, 128);
-    mbar_init(a_free, 1);
+    mbar_init(a_full, NFEAT);
+    mbar_init(a_free, 2);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   if (!MAX_ONLY)
-    for (int i = tid; i < 128 * 16; i += 192)
-      reinterpret_cast<__nv_bfloat16*>(smem + OFF_ONES)[i] = __float2bfloat16(1.0f);
+    for (int i = tid; i < 2 * 8192; i += NTHREADS) {   // the "ones" block of both stages (16 KB each, bf16 1.0)
+      const int s = i / 8192, j = i % 8192;
+      reinterpret_cast<__nv_bfloat16*>(smem + OFF_STAGE + s * STAGE_BYTES + 32768)[j] = __float2bfloat16(1.0f);
+    }
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tb = *tmem_slot;
 
-  if (warp == 4) {
+  // a tile whose rows all enter the summary and hold real keys is stored to the workspace by one bulk copy
+  auto tile_is_plain = [&](int i) {
+    const int row0 = (t_lo + i) * TILE;
+    return row0 >= a.sum_lo && row0 + TILE <= a.sum_hi && a.k_pos0 + row0 + TILE <= len_b;
+  };
+
+  if (warp == 8) {
     // ---------------- producer ----------------
-    if (lane == 0) {
+    const bool leader = elect_one();
+    if (leader) {
       prefetch_tmap(&a.tm_k);
       prefetch_tmap(&a.tm_v);
       prefetch_tmap(&a.tm_w);
+      prefetch_tmap(&a.tm_phik);
       mbar_expect_tx(bar_w, 16384);
       tma_load_2d(smem + OFF_W, &a.tm_w, bar_w, 0, 0);
-      for (int i = 0; i < nt; ++i) {
-        const int s = i & 1;
-        if (i >= 2) mbar_wait(empty + s, ((i >> 1) - 1) & 1, a.status, 11);
+    }
+    for (int i = 0; i < nt; ++i) {
+      const int s = i & 1;
+      if (i >= 2) mbar_wait(empty + s, ((i >> 1) - 1) & 1, a.status, 11);
+      if (leader) {
         uint8_t* st = smem + OFF_STAGE + s * STAGE_BYTES;
         const int row0 = (t_lo + i) * TILE;
         mbar_expect_tx(full + s, MAX_ONLY ? 16384 : 32768);
@@ -181,69 +225,87 @@ __global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ Ke
         if (!MAX_ONLY) tma_load_4d(st + 16384, &a.tm_v, full + s, 0, row0, h, b);
       }
     }
-  } else if (warp == 5) {
+    __syncwarp();
+  } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      const uint32_t id_uk = idesc_bf16(128, 128, false, false);
-      const uint32_t id_kv = idesc_bf16(128, 64, true, true);
-      const uint32_t id_ks = idesc_bf16(128, 16, true, true);
-      const uint32_t sW = smem_u32(smem + OFF_W), sA = smem_u32(smem + OFF_A), sOnes = smem_u32(smem + OFF_ONES);
-      auto issue_kv = [&](int u) {
-        mbar_wait(a_full, u & 1, a.status, 12);
-        tc_fence_after_sync();
-        const uint32_t sV = smem_u32(smem + OFF_STAGE + (u & 1) * STAGE_BYTES + 16384);
+    const bool leader = elect_one();
+    constexpr uint32_t id_uk = idesc_bf16(128, 128, false, false);
+    constexpr uint32_t id_kv = idesc_bf16(128, 80, true, true);
+    const uint64_t dW = smem_desc_sw128(smem_u32(smem + OFF_W), 16, 1024);
+    const uint64_t dA = smem_desc_sw128(smem_u32(smem + OFF_A), 16384, 1024);
+    const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_STAGE), 16, 1024);
+    const uint64_t dV0 = smem_desc_sw128(smem_u32(smem + OFF_STAGE + 16384), 16384, 1024);  // second MN block = ones
+    auto issue_kv = [&](int u) {
+      const int s = u & 1;
+      mbar_wait(a_full, u & 1, a.status, 12);
+      tc_fence_after_sync();
+      if (leader) {
+        const bool plain = tile_is_plain(u);
+        if (plain) {
+          const int row0 = (t_lo + u) * TILE;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) tma_store_3d(&a.tm_phik, smem + OFF_A + j * 16384, j * 64, row0, bh);
+          tma_store_commit();
+        }
+        const uint64_t dV = dV0 + (uint64_t)(s * (STAGE_BYTES >> 4));
 #pragma unroll
         for (int mb = 0; mb < 2; ++mb)
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint64_t da = smem_desc_sw128(sA + mb * 32768 + k * 2048, 16384, 1024);
-            mma_ss(tb + T_KV + mb * 64, da, smem_desc_sw128(sV + k * 2048, 16, 1024), id_kv, (u > 0) || (k > 0));
-            mma_ss(tb + T_KS + mb * 16, da, smem_desc_sw32(sOnes + k * 512, 16, 256), id_ks, (u > 0) || (k > 0));
-          }
+          for (int k = 0; k < 8; ++k)
+            mma_ss(tb + T_KV + mb * 128, dA + (uint64_t)(mb * (32768 >> 4) + k * (2048 >> 4)),
+                   dV + (uint64_t)(k * (2048 >> 4)), id_kv, (u > 0) || (k > 0));
         mma_commit(a_free);
-        mma_commit(empty + (u & 1));
-      };
-      mbar_wait(bar_w, 0, a.status, 13);
-      for (int i = 0; i < nt; ++i) {
-        const int s = i & 1;
-        mbar_wait(full + s, (i >> 1) & 1, a.status, 14);
-        if (i >= 2) mbar_wait(uk_free + s, ((i >> 1) - 1) & 1, a.status, 15);
-        tc_fence_after_sync();
-        const uint32_t sK = smem_u32(smem + OFF_STAGE + s * STAGE_BYTES);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_ss(tb + T_UK + s * 128, smem_desc_sw128(sK + k * 32, 16, 1024), smem_desc_sw128(sW + k * 32, 16, 1024),
-                 id_uk, k > 0);
-        mma_commit(uk_full + s);
-        if (MAX_ONLY) {
-          // the K stage is free once U is computed and the row norms were read (uk_free)
-        } else if (i >= 1) {
-          issue_kv(i - 1);
-        }
+        mma_commit(empty + s);
+        if (plain) tma_store_wait_read();
+        mbar_arrive(a_free);
       }
-      if (!MAX_ONLY && nt > 0) issue_kv(nt - 1);
-      mma_commit(bar_done);
+      __syncwarp();
+    };
+    mbar_wait(bar_w, 0, a.status, 13);
+    for (int i = 0; i < nt; ++i) {
+      const int s = i & 1;
+      mbar_wait(full + s, (i >> 1) & 1, a.status, 14);
+      if (i >= 2) mbar_wait(uk_free + s, ((i >> 1) - 1) & 1, a.status, 15);
+      tc_fence_after_sync();
+      if (leader) {
+        const uint64_t dK = dK0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+        const uint32_t td = tb + T_UK + s * 128;
+        mma_ss(td, dK, dW, id_uk, false);
+        mma_ss(td, dK + 2, dW + 2, id_uk, true);
+        mma_ss(td, dK + 4, dW + 4, id_uk, true);
+        mma_ss(td, dK + 6, dW + 6, id_uk, true);
+        mma_commit(uk_full + s);
+      }
+      __syncwarp();
+      if (!MAX_ONLY && i >= 1) issue_kv(i - 1);
     }
+    if (!MAX_ONLY && nt > 0) issue_kv(nt - 1);
+    if (leader) {
+      mma_commit(bar_done);
+      if (!MAX_ONLY) tma_store_wait_all();
+    }
+    __syncwarp();
   } else {
-    // ---------------- feature warps: thread <-> key row ----------------
-    const uint32_t lane_base = tb + ((uint32_t)(warp * 32) << 16);
-    const int64_t len_b = a.lengths ? min(a.lengths[b], a.S_total) : a.S_total;
+    // ---------------- feature warps ----------------
+    const int qd = warp & 3, hf = warp >> 2;
+    const int krow = qd * 32 + lane;                 // key row inside the tile
+    const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
     const float beta = MAX_ONLY ? 0.f : a.beta_in[bh];
     float run_max = -INFINITY;
     for (int i = 0; i < nt; ++i) {
       const int s = i & 1;
-      const int row = (t_lo + i) * TILE + tid;
+      const int row = (t_lo + i) * TILE + krow;
       mbar_wait(full + s, (i >> 1) & 1, a.status, 19);
+      const uint8_t* sK = smem + OFF_STAGE + s * STAGE_BYTES;
+      const float g = 0.5f * a.tau * row_sumsq_sw128(sK, krow);
       mbar_wait(uk_full + s, (i >> 1) & 1, a.status, 16);
       tc_fence_after_sync();
-      const uint8_t* sK = smem + OFF_STAGE + s * STAGE_BYTES;
-      const float g = 0.5f * a.tau * row_sumsq_sw128(sK, tid);
       if (MAX_ONLY) {
         float mx = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld32(lane_base + T_UK + s * 128 + c * 32, r);
+          tmem_ld32(lane_base + T_UK + s * 128 + 64 * hf + 32 * c, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fabsf(__uint_as_float(r[j])));
@@ -251,23 +313,23 @@ __global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ Ke
         if (row >= a.sum_lo && row < a.sum_hi) run_max = fmaxf(run_max, (mx - g) - a.half_log_m);
         tc_fence_before_sync();
         mbar_arrive(uk_free + s);
-        // MAX mode has no KV MMA to release the stage: the last reader does
+        // MAX mode has no summary MMA to release the stage: the last reader does
         if (i + 2 < nt) {
-          // all 128 rows must have read their K row before the stage is refilled
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync 1, 256;" ::: "memory");   // every row has read its K row and its U values
           if (tid == 0) mbar_arrive(empty + s);
         }
       } else {
-        if (i >= 1) mbar_wait(a_free, (i - 1) & 1, a.status, 17);
         const bool live = row < a.S && (a.k_pos0 + row) < len_b;
         const bool in_sum = live && row >= a.sum_lo && row < a.sum_hi;
+        const bool plain = tile_is_plain(i);
         const float off = ((-g - a.half_log_m) - beta) * kLog2e;
         __nv_bfloat16* grow = a.phik + ((int64_t)bh * a.S + row) * kM;
         uint8_t* sA = smem + OFF_A;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
+          const int f0 = 64 * hf + 32 * c;           // first projection of this chunk
           uint32_t r[32];
-          tmem_ld32(lane_base + T_UK + s * 128 + c * 32, r);
+          tmem_ld32(lane_base + T_UK + s * 128 + f0, r);
           tmem_ld_wait();
           uint32_t p1[16], p2[16];
 #pragma unroll
@@ -276,23 +338,26 @@ __global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ Ke
             p1[j] = live ? pack_bf16(ex2(u0 + off), ex2(u1 + off)) : 0u;
             p2[j] = live ? pack_bf16(ex2(off - u0), ex2(off - u1)) : 0u;
           }
-          if (row < a.S) {
+          if (!plain && row < a.S) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              reinterpret_cast<uint4*>(grow + 32 * c)[q] = make_uint4(p1[4 * q], p1[4 * q + 1], p1[4 * q + 2], p1[4 * q + 3]);
-              reinterpret_cast<uint4*>(grow + kR + 32 * c)[q] =
+              reinterpret_cast<uint4*>(grow + f0)[q] = make_uint4(p1[4 * q], p1[4 * q + 1], p1[4 * q + 2], p1[4 * q + 3]);
+              reinterpret_cast<uint4*>(grow + kR + f0)[q] =
                   make_uint4(p2[4 * q], p2[4 * q + 1], p2[4 * q + 2], p2[4 * q + 3]);
             }
           }
+          // the previous tile's MMAs and bulk store must be done with the shared phi(K) buffer
+          if (c == 0 && i >= 1) mbar_wait(a_free, (i - 1) & 1, a.status, 17);
           // MN-major A operand: block = feature / 64, 16-byte chunk = (feature % 64) / 8, swizzled by key % 8
+          const int blk = f0 >> 6;                   // = hf
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const int chunk = (c & 1) * 4 + q;
-            const uint32_t o = (uint32_t)tid * 128u + (uint32_t)((chunk ^ (tid & 7)) << 4);
+            const int chunk = ((f0 & 63) >> 3) + q;
+            const uint32_t o = (uint32_t)krow * 128u + (uint32_t)((chunk ^ (krow & 7)) << 4);
             const uint4 z = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(sA + (c >> 1) * 16384 + o) =
+            *reinterpret_cast<uint4*>(sA + blk * 16384 + o) =
                 in_sum ? make_uint4(p1[4 * q], p1[4 * q + 1], p1[4 * q + 2], p1[4 * q + 3]) : z;
-            *reinterpret_cast<uint4*>(sA + (2 + (c >> 1)) * 16384 + o) =
+            *reinterpret_cast<uint4*>(sA + (2 + blk) * 16384 + o) =
                 in_sum ? make_uint4(p2[4 * q], p2[4 * q + 1], p2[4 * q + 2], p2[4 * q + 3]) : z;
           }
         }
@@ -306,40 +371,33 @@ __global__ void __launch_bounds__(192) tc_keys_kernel(const __grid_constant__ Ke
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) run_max = fmaxf(run_max, __shfl_xor_sync(0xffffffffu, run_max, o));
       if (lane == 0) red[warp] = run_max;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (tid == 0) {
-        const float v = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        float v = red[0];
+        for (int i = 1; i < 8; ++i) v = fmaxf(v, red[i]);
         if (v > -INFINITY) atomic_max_float(a.beta_out + bh, v);
       }
     } else {
       mbar_wait(bar_done, 0, a.status, 18);
       tc_fence_after_sync();
+      // thread (feature row, half): half 0 writes KV columns 0-31, half 1 columns 32-63 and the feature sum
       float* part = a.partial + ((int64_t)bh * a.nsplit + split) * kM * 65;
 #pragma unroll
       for (int mb = 0; mb < 2; ++mb) {
-        float* prow = part + (int64_t)(mb * 128 + tid) * 65;
-        if (nt > 0) {
+        float* prow = part + (int64_t)(mb * 128 + krow) * 65;
+        uint32_t r[32], q[16];
+        tmem_ld32(lane_base + T_KV + mb * 128 + 32 * hf, r);
+        tmem_ld16(lane_base + T_KV + mb * 128 + 64, q);
+        tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + T_KV + mb * 64 + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) prow[c * 32 + j] = __uint_as_float(r[j]);
-          }
-          uint32_t q[16];
-          tmem_ld16(lane_base + T_KS + mb * 16, q);
-          tmem_ld_wait();
-          prow[64] = __uint_as_float(q[0]);
-        } else {
-          for (int j = 0; j < 65; ++j) prow[j] = 0.f;
-        }
+        for (int j = 0; j < 32; ++j) prow[32 * hf + j] = nt > 0 ? __uint_as_float(r[j]) : 0.f;
+        if (hf == 1) prow[64] = nt > 0 ? __uint_as_float(q[0]) : 0.f;
       }
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     tmem_dealloc(tb, 512);
   }
@@ -352,29 +410,41 @@ struct BandArgs {
   SblParams p;
   const float* beta;
   const float* ksum;
+  const float* wmax;     // [1]: max_f |sqrt(tau) w_f| of the bf16 projection
   int* status;
 };
 
+#ifdef SBL_TRACE
+__device__ long long g_trace[64][32];
+__device__ long long g_trace2[64][2][32];   // [cta][0 = producer, 1 = MMA issuer][slot]
+#define TRACE(slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (tid == 0)) g_trace[blockIdx.y * 8 + blockIdx.x][slot] = clock64(); } while (0)
+#define TRACE2(who, slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (slot) < 32) g_trace2[blockIdx.y * 8 + blockIdx.x][who][slot] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#define TRACE2(who, slot) do { } while (0)
+#endif
+
 namespace band {
-constexpr int BQ = 128, KT = 64, NS = 3;
-constexpr uint32_t OFF_Q = 0;          // 16 KB [128 q][64 e]
-constexpr uint32_t OFF_W = 16384;      // 16 KB [128 r][64 e]
-constexpr uint32_t OFF_KV = 32768;     // 32 KB [256 f][64 d]
-constexpr uint32_t OFF_STAGE = 65536;  // NS x { K 8 KB, V 8 KB, phi(K) 4 x 8 KB }
-constexpr uint32_t STAGE_BYTES = 49152;
-constexpr uint32_t OFF_KSUM = OFF_STAGE + NS * STAGE_BYTES;  // 1 KB fp32[256]
-constexpr uint32_t OFF_BAR = OFF_KSUM + 1024;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr int BQ = 128, KT = 128;
+constexpr int NSOFT = 256;                 // softmax threads: warps 0-7; warp w owns rows 32*(w%4).., column half w/4
+constexpr int NTHREADS = NSOFT + 64;       // + producer warp 8 + MMA warp 9
+constexpr uint32_t OFF_Q = 0;              // 16 KB [128 q][64 e]
+constexpr uint32_t OFF_KV = 16384;         // 32 KB [256 f][64 d]; its first 16 KB hold Wt [128 r][64 e] until U is computed
+constexpr uint32_t OFF_K = 49152;          // 16 KB [128 keys][64 e]
+constexpr uint32_t OFF_V = OFF_K + 16384;  // 16 KB [128 keys][64 d]
+constexpr uint32_t OFF_PK = OFF_V + 16384; // 2 x 64 KB: phi(K) tiles, each 4 blocks [128 keys][64 f]
+constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + exchange fp32[3][256]
+constexpr uint32_t OFF_BAR = OFF_MISC + 4096;
+constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;
 // tensor memory columns
 constexpr uint32_t T_PHIQ = 0;     // 128: phi(Q) packed bf16 (256 features)
-constexpr uint32_t T_SP = 128;     // 2 x { S 64, P 64 }
+constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, later P of the same tile
 constexpr uint32_t T_O = 384;      // 64
-constexpr uint32_t T_D = 448;      // 2 x 32: D packed bf16 (64 keys)
-constexpr uint32_t T_UQ = 128;     // 128, aliases S/P before the band loop
-constexpr uint32_t T_LR = 128;     // 64, aliases S[0] after the band loop
+constexpr uint32_t T_D = 448;      // 64: D packed bf16 (128 keys)
+constexpr uint32_t T_UQ = 128;     // aliases buffer 0 before the band loop
 }  // namespace band
 
-__global__ void __launch_bounds__(192) tc_band_kernel(const __grid_constant__ BandArgs a) {
+__global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_constant__ BandArgs a) {
   using namespace band;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -384,22 +454,27 @@ __global__ void __launch_bounds__(192) tc_band_kernel(const __grid_constant__ Ba
   uint64_t* bar_uq = bars + 2;
   uint64_t* bar_phiq = bars + 3;
   uint64_t* bar_lr = bars + 4;
-  uint64_t* full = bars + 5;       // [NS]
-  uint64_t* empty = bars + 8;      // [NS]
-  uint64_t* sp_full = bars + 11;   // [2]
-  uint64_t* sp_free = bars + 13;   // [2]
-  uint64_t* d_full = bars + 15;    // [2]
-  uint64_t* d_free = bars + 17;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
-  float* red = reinterpret_cast<float*>(bars + 20);  // [4]
-  float* s_ksum = reinterpret_cast<float*>(smem + OFF_KSUM);
+  uint64_t* d_free = bars + 5;
+  uint64_t* k_full = bars + 6;
+  uint64_t* k_empty = bars + 8;
+  uint64_t* v_full = bars + 10;
+  uint64_t* v_empty = bars + 12;
+  uint64_t* s_full = bars + 14;     // [2]
+  uint64_t* a_done = bars + 16;     // [2]
+  uint64_t* p_full = bars + 18;     // [2]
+  uint64_t* b_done = bars + 20;     // [2]
+  uint64_t* pk_full = bars + 22;    // [2]
+  uint64_t* pk_empty = bars + 28;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
+  float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);
+  float* s_xch = s_ksum + kM;       // [3][256]
 
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int i0 = blockIdx.x * BQ;
   const int hw = p.w / 2;
-  int len_b = (int)(p.key_lengths ? min(p.key_lengths[b], p.S_total) : p.S_total);
+  const int len_b = (int)(p.key_lengths ? min(p.key_lengths[b], p.S_total) : p.S_total);
   // key buffer rows any query of this tile can see, clipped to the buffer and to the key length
   const int nq = min(BQ, p.T - i0);
   int lo = (int)(p.q_pos0 + i0 - hw - p.k_pos0);
@@ -413,33 +488,39 @@ __global__ void __launch_bounds__(192) tc_band_kernel(const __grid_constant__ Ba
     mbar_init(bar_qw, 1);
     mbar_init(bar_kv, 1);
     mbar_init(bar_uq, 1);
-    mbar_init(bar_phiq, 128);
+    mbar_init(bar_phiq, NSOFT);
     mbar_init(bar_lr, 1);
-    for (int i = 0; i < NS; ++i) {
-      mbar_init(full + i, 1);
-      mbar_init(empty + i, 1);
-    }
+    mbar_init(d_free, 1);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(sp_full + i, 1);
-      mbar_init(sp_free + i, 128);
-      mbar_init(d_full + i, 128);
-      mbar_init(d_free + i, 1);
+      mbar_init(pk_full + i, 1);
+      mbar_init(pk_empty + i, 1);
+      mbar_init(s_full + i, 1);
+      mbar_init(a_done + i, NSOFT);
+      mbar_init(p_full + i, 1);
+      mbar_init(b_done + i, NSOFT);
     }
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  for (int i = tid; i < kM; i += 192) s_ksum[i] = a.ksum[(int64_t)bh * kM + i];
+  if (tid == 0) TRACE(0);
+  for (int i = tid; i < kM; i += NTHREADS) s_ksum[i] = a.ksum[(int64_t)bh * kM + i];
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tb = *tmem_slot;
+  if (tid == 0) TRACE(1);
 
-  if (warp == 4) {
-    // ---------------- producer ----------------
-    if (lane == 0) {
+  if (warp == 8) {
+    // ---------------- producer (whole warp waits, one lane issues) ----------------
+    const bool leader = elect_one();
+    if (leader) {
       prefetch_tmap(&a.tm_q);
       prefetch_tmap(&a.tm_k);
       prefetch_tmap(&a.tm_v);
@@ -448,131 +529,176 @@ __global__ void __launch_bounds__(192) tc_band_kernel(const __grid_constant__ Ba
       prefetch_tmap(&a.tm_kv);
       mbar_expect_tx(bar_qw, 32768);
       tma_load_4d(smem + OFF_Q, &a.tm_q, bar_qw, 0, i0, h, b);
-      tma_load_2d(smem + OFF_W, &a.tm_w, bar_qw, 0, 0);
-      mbar_expect_tx(bar_kv, 32768);
-      tma_load_3d(smem + OFF_KV, &a.tm_kv, bar_kv, 0, 0, bh);
-      for (int t = 0; t < nt; ++t) {
-        const int s = t % NS;
-        if (t >= NS) mbar_wait(empty + s, ((t / NS) - 1) & 1, a.status, 21);
-        uint8_t* st = smem + OFF_STAGE + s * STAGE_BYTES;
-        const int row0 = j0 + t * KT;
-        mbar_expect_tx(full + s, STAGE_BYTES);
-        tma_load_4d(st, &a.tm_k, full + s, 0, row0, h, b);
-        tma_load_4d(st + 8192, &a.tm_v, full + s, 0, row0, h, b);
+      tma_load_2d(smem + OFF_KV, &a.tm_w, bar_qw, 0, 0);
+    }
+    // K and V are single-buffered, phi(K) double-buffered.  Issue order follows the order
+    // in which the tensor core frees the buffers: K(t), phi(K)(t), then V(t-1).
+    auto load_v = [&](int t) {
+      if (t >= 1) mbar_wait(v_empty, (t - 1) & 1, a.status, 23);
+      if (leader) {
+        mbar_expect_tx(v_full, 16384);
+        tma_load_4d(smem + OFF_V, &a.tm_v, v_full, 0, j0 + t * KT, h, b);
+        TRACE2(0, 6 + 8 * t);
+      }
+    };
+    for (int t = 0; t < nt; ++t) {
+      const int s = t & 1, row0 = j0 + t * KT;
+      if (t >= 1) mbar_wait(k_empty, (t - 1) & 1, a.status, 21);
+      if (leader) {
+        mbar_expect_tx(k_full, 16384);
+        tma_load_4d(smem + OFF_K, &a.tm_k, k_full, 0, row0, h, b);
+        TRACE2(0, 1 + 8 * t);
+      }
+      if (t >= 2) mbar_wait(pk_empty + s, ((t >> 1) - 1) & 1, a.status, 22);
+      if (leader) {
+        mbar_expect_tx(pk_full + s, 65536);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tma_load_3d(st + 16384 + j * 8192, &a.tm_phik, full + s, j * 64, row0, bh);
+        for (int j = 0; j < 4; ++j)
+          tma_load_3d(smem + OFF_PK + s * 65536 + j * 16384, &a.tm_phik, pk_full + s, j * 64, row0, bh);
+        TRACE2(0, 2 + 8 * t);
+      }
+      if (t == 0) {
+        load_v(0);
+        // KV shares its buffer with Wt: load it once U = Q Wt^T has been computed
+        mbar_wait(bar_uq, 0, a.status, 24);
+        if (leader) {
+          mbar_expect_tx(bar_kv, 32768);
+          tma_load_3d(smem + OFF_KV, &a.tm_kv, bar_kv, 0, 0, bh);
+        }
+      } else if (t >= 2) {
+        load_v(t - 1);
       }
     }
-  } else if (warp == 5) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      const uint32_t id_uq = idesc_bf16(128, 128, false, false);
-      const uint32_t id_s = idesc_bf16(128, 64, false, false);
-      const uint32_t id_o = idesc_bf16(128, 64, false, true);
-      const uint32_t sQ = smem_u32(smem + OFF_Q), sW = smem_u32(smem + OFF_W), sKV = smem_u32(smem + OFF_KV);
-      auto issue_o = [&](int u) {
-        const int bu = u & 1, su = u % NS;
-        mbar_wait(d_full + bu, (u >> 1) & 1, a.status, 22);
-        tc_fence_after_sync();
-        const uint32_t sV = smem_u32(smem + OFF_STAGE + su * STAGE_BYTES + 8192);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_ts(tb + T_O, tb + T_D + bu * 32 + k * 8, smem_desc_sw128(sV + k * 2048, 16, 1024), id_o,
-                 (u > 0) || (k > 0));
-        mma_commit(empty + su);
-        mma_commit(d_free + bu);
-      };
-      mbar_wait(bar_qw, 0, a.status, 23);
+    if (nt >= 2) load_v(nt - 1);
+    if (nt == 0) {
+      mbar_wait(bar_uq, 0, a.status, 24);
+      if (leader) {
+        mbar_expect_tx(bar_kv, 32768);
+        tma_load_3d(smem + OFF_KV, &a.tm_kv, bar_kv, 0, 0, bh);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // ---------------- MMA issuer (whole warp waits, one lane issues) ----------------
+    const bool leader = elect_one();
+    constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
+    constexpr uint32_t id_o = idesc_bf16(128, 64, false, true);
+    const uint64_t dQ = smem_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
+    const uint64_t dKV = smem_desc_sw128(smem_u32(smem + OFF_KV), 16, 1024);
+    const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_K), 16, 1024);
+    const uint64_t dV0 = smem_desc_sw128(smem_u32(smem + OFF_V), 16, 1024);
+    const uint64_t dPK0 = smem_desc_sw128(smem_u32(smem + OFF_PK), 16, 1024);
+    auto issue_s = [&](int t) {
+      const int s = t & 1;
+      mbar_wait(k_full, t & 1, a.status, 25);
       tc_fence_after_sync();
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        mma_ss(tb + T_UQ, smem_desc_sw128(sQ + k * 32, 16, 1024), smem_desc_sw128(sW + k * 32, 16, 1024), id_uq,
-               k > 0);
-      mma_commit(bar_uq);
-      mbar_wait(bar_phiq, 0, a.status, 24);
+      if (leader) {
+        TRACE2(1, 1 + 8 * t);
+        const uint32_t td = tb + T_BUF + s * 128;
+        mma_ss(td, dQ, dK0, id_n128, false);
+        mma_ss(td, dQ + 2, dK0 + 2, id_n128, true);
+        mma_ss(td, dQ + 4, dK0 + 4, id_n128, true);
+        mma_ss(td, dQ + 6, dK0 + 6, id_n128, true);
+        mma_commit(k_empty);
+        mma_commit(s_full + s);
+      }
+      __syncwarp();
+    };
+    auto issue_p = [&](int t) {
+      const int s = t & 1;
+      mbar_wait(a_done + s, (t >> 1) & 1, a.status, 26);
+      mbar_wait(pk_full + s, (t >> 1) & 1, a.status, 27);
       tc_fence_after_sync();
-      for (int t = 0; t < nt; ++t) {
-        const int s = t % NS, bb = t & 1;
-        mbar_wait(full + s, (t / NS) & 1, a.status, 25);
-        if (t >= 2) mbar_wait(sp_free + bb, ((t >> 1) - 1) & 1, a.status, 26);
-        tc_fence_after_sync();
-        const uint32_t sK = smem_u32(smem + OFF_STAGE + s * STAGE_BYTES);
-        const uint32_t sPK = sK + 16384;
-        const uint32_t tS = tb + T_SP + bb * 128, tP = tS + 64;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_ss(tS, smem_desc_sw128(sQ + k * 32, 16, 1024), smem_desc_sw128(sK + k * 32, 16, 1024), id_s, k > 0);
+      if (leader) {
+        TRACE2(1, 2 + 8 * t);
+        const uint64_t dPK = dPK0 + (uint64_t)(s * (65536 >> 4));
+        const uint32_t td = tb + T_BUF + s * 128;
 #pragma unroll
         for (int k = 0; k < 16; ++k)
-          mma_ts(tP, tb + T_PHIQ + k * 8, smem_desc_sw128(sPK + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024), id_s,
-                 k > 0);
-        mma_commit(sp_full + bb);
-        if (t >= 1) issue_o(t - 1);
+          mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
+        mma_commit(pk_empty + s);
+        mma_commit(p_full + s);
       }
-      if (nt > 0) issue_o(nt - 1);
-      // low-rank numerator LR = phi(Q) KV into the (now idle) S[0] columns
-      mbar_wait(bar_kv, 0, a.status, 27);
+      __syncwarp();
+    };
+    auto issue_o = [&](int u) {
+      const int s = u & 1;
+      mbar_wait(b_done + s, (u >> 1) & 1, a.status, 28);
+      mbar_wait(v_full, u & 1, a.status, 29);
       tc_fence_after_sync();
+      if (leader) {
+        TRACE2(1, 7 + 8 * u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_ts(tb + T_O, tb + T_D + k * 8, dV0 + (uint64_t)(k * (2048 >> 4)), id_o, true);
+        mma_commit(v_empty);
+        mma_commit(d_free);
+      }
+      __syncwarp();
+    };
+    mbar_wait(bar_qw, 0, a.status, 30);
+    tc_fence_after_sync();
+    if (leader) {
+      TRACE2(1, 0);
+      mma_ss(tb + T_UQ, dQ, dKV, id_n128, false);
+      mma_ss(tb + T_UQ, dQ + 2, dKV + 2, id_n128, true);
+      mma_ss(tb + T_UQ, dQ + 4, dKV + 4, id_n128, true);
+      mma_ss(tb + T_UQ, dQ + 6, dKV + 6, id_n128, true);
+      mma_commit(bar_uq);
+    }
+    __syncwarp();
+    mbar_wait(bar_phiq, 0, a.status, 31);
+    tc_fence_after_sync();
+    if (nt > 0) issue_s(0);
+    if (nt > 1) issue_s(1);
+    // O starts as the low-rank numerator phi(Q) KV; the band tiles accumulate onto it
+    mbar_wait(bar_kv, 0, a.status, 32);
+    tc_fence_after_sync();
+    if (leader) {
 #pragma unroll
       for (int k = 0; k < 16; ++k)
-        mma_ts(tb + T_LR, tb + T_PHIQ + k * 8, smem_desc_sw128(sKV + k * 2048, 16, 1024), id_o, k > 0);
-      mma_commit(bar_lr);
+        mma_ts(tb + T_O, tb + T_PHIQ + k * 8, dKV + (uint64_t)(k * (2048 >> 4)), id_o, k > 0);
     }
-  } else {
-    // ---------------- softmax warps: thread <-> query row ----------------
-    const uint32_t lane_base = tb + ((uint32_t)(warp * 32) << 16);
-    const int gi = (int)p.q_pos0 + i0 + tid;  // global query position
-    // max |k|^2 over the keys this tile visits (rows of the key buffer)
-    float kmax2 = 0.f;
-    {
-      const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(p.k) + b * p.k_stride_b + h * p.k_stride_h;
-      for (int rr = tid; rr < nt * KT; rr += 128) {
-        const int row = j0 + rr;
-        if (row < p.S) {
-          const uint4* src = reinterpret_cast<const uint4*>(kb + (int64_t)row * p.k_stride_s);
-          float s = 0.f;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 v = __ldg(src + c);
-            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float x = bf16_lo(wv[j]), y = bf16_hi(wv[j]);
-              s = fmaf(x, x, s);
-              s = fmaf(y, y, s);
-            }
-          }
-          kmax2 = fmaxf(kmax2, s);
+    __syncwarp();
+    for (int t = 0; t < nt; ++t) {
+      issue_p(t);
+      if (t >= 1) {
+        // both need B(t-1) finished; S first, the softmax warps are waiting for it
+        if (t + 1 < nt) {
+          mbar_wait(b_done + ((t - 1) & 1), ((t - 1) >> 1) & 1, a.status, 28);
+          issue_s(t + 1);
         }
+        issue_o(t - 1);
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) kmax2 = fmaxf(kmax2, __shfl_xor_sync(0xffffffffu, kmax2, o));
-      if (lane == 0) red[warp] = kmax2;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      kmax2 = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     }
-    // ---- phi(Q) ----
-    mbar_wait(bar_qw, 0, a.status, 32);
-    mbar_wait(bar_uq, 0, a.status, 28);
-    tc_fence_after_sync();
-    const float qn2 = row_sumsq_sw128(smem + OFF_Q, tid);
+    if (nt > 0) issue_o(nt - 1);
+    if (leader) {
+      mma_commit(bar_lr);
+      TRACE2(1, 31);
+    }
+    __syncwarp();
+  } else {
+    // ---------------- softmax warps ----------------
+    const int qd = warp & 3, hf = warp >> 2;         // lane quarter (rows), column half
+    const int row = qd * 32 + lane;                  // query row of this thread
+    const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
+    const int gi = (int)p.q_pos0 + i0 + row;         // global query position
+    // ---- phi(Q): this thread's 64 projections -> 128 features ----
+    mbar_wait(bar_qw, 0, a.status, 33);
+    const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
     const float g = 0.5f * p.softmax_temp * qn2;
-    float M = 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(lane_base + T_UQ + c * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) M = fmaxf(M, fabsf(__uint_as_float(r[j])));
-    }
-    float Z = 0.f;
+    const float M = sqrtf(qn2) * __ldg(a.wmax);      // >= |u_f| for every feature (Cauchy-Schwarz)
+    mbar_wait(bar_uq, 0, a.status, 34);
+    tc_fence_after_sync();
+    TRACE(3);
+    float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
     {
       const float mo = -M * kLog2e;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
+        const int f0 = 64 * hf + 32 * c;             // first projection index of this chunk
         uint32_t r[32];
-        tmem_ld32(lane_base + T_UQ + c * 32, r);
+        tmem_ld32(lane_base + T_UQ + f0, r);
         tmem_ld_wait();
         uint32_t p1[16], p2[16];
 #pragma unroll
@@ -581,92 +707,154 @@ __global__ void __launch_bounds__(192) tc_band_kernel(const __grid_constant__ Ba
           p1[j] = pack_bf16(ex2(u0 + mo), ex2(u1 + mo));
           p2[j] = pack_bf16(ex2(mo - u0), ex2(mo - u1));
           // Z from the rounded features, so that Z - dps cancels what the MMA sees
-          Z = fmaf(bf16_lo(p1[j]), s_ksum[32 * c + 2 * j], Z);
-          Z = fmaf(bf16_hi(p1[j]), s_ksum[32 * c + 2 * j + 1], Z);
-          Z = fmaf(bf16_lo(p2[j]), s_ksum[kR + 32 * c + 2 * j], Z);
-          Z = fmaf(bf16_hi(p2[j]), s_ksum[kR + 32 * c + 2 * j + 1], Z);
+          z0 = fmaf(bf16_lo(p1[j]), s_ksum[f0 + 2 * j], z0);
+          z1 = fmaf(bf16_hi(p1[j]), s_ksum[f0 + 2 * j + 1], z1);
+          z2 = fmaf(bf16_lo(p2[j]), s_ksum[kR + f0 + 2 * j], z2);
+          z3 = fmaf(bf16_hi(p2[j]), s_ksum[kR + f0 + 2 * j + 1], z3);
         }
-        // the U columns are dead after this pass; phi(Q) lives in its own columns
-        tmem_st16(lane_base + T_PHIQ + 16 * c, p1);
-        tmem_st16(lane_base + T_PHIQ + 64 + 16 * c, p2);
+        tmem_st16(lane_base + T_PHIQ + f0 / 2, p1);
+        tmem_st16(lane_base + T_PHIQ + 64 + f0 / 2, p2);
       }
       tmem_st_wait();
     }
     tc_fence_before_sync();
     mbar_arrive(bar_phiq);
+    TRACE(4);
 
     const float half_log_m = 0.5f * logf((float)kM);
-    const float pls = (-g + M - half_log_m) + a.beta[bh];
-    const float cstab = p.softmax_temp * sqrtf(qn2 * kmax2);       // >= tau q.k for every visited key
-    const float psc = ex2((pls - cstab) * kLog2e);                 // e^{pls - c}
-    const float sc = p.softmax_temp * kLog2e, co = -cstab * kLog2e;
+    const float pls = (-g + M - half_log_m) + a.beta[bh];          // query log-scale + key log-scale
+    const float sc = p.softmax_temp * kLog2e, co = -pls * kLog2e;  // exp(tau s - pls) = ex2(s * sc + co)
     float L = 0.f, dps = 0.f;
-    for (int t = 0; t < nt; ++t) {
-      const int bb = t & 1;
-      mbar_wait(sp_full + bb, (t >> 1) & 1, a.status, 29);
-      if (t >= 2) mbar_wait(d_free + bb, ((t >> 1) - 1) & 1, a.status, 30);
-      tc_fence_after_sync();
-      const uint32_t tS = lane_base + T_SP + bb * 128, tP = tS + 64, tD = lane_base + T_D + bb * 32;
-      const int gk0 = (int)p.k_pos0 + j0 + t * KT;   // global position of column 0
+    uint32_t Ec[32], En[32];   // exp(tau S - pls), packed bf16: tile being finished / tile just started
+
+    // valid tile-local columns of this row in tile t: [clo, chi]
+    auto col_range = [&](int t, int& clo, int& chi) {
+      const int gk0 = (int)p.k_pos0 + j0 + t * KT;
+      clo = max(gi - hw - gk0, 0);
+      chi = min(min(gi - hw + p.w - 1 - gk0, len_b - 1 - gk0), KT - 1);
+    };
+    // Software pipeline over key tiles: A(t+1) (exponentials of S) runs while the
+    // tensor core computes P(t); B(t) then forms D(t).
+    for (int t = -1; t < nt; ++t) {
+      if (t + 1 < nt) {
+        // A: S(t+1) -> masked exponentials (kept packed), row sum L
+        const int u = t + 1, s = u & 1;
+        int clo, chi;
+        col_range(u, clo, chi);
+        const int wlo = __reduce_min_sync(0xffffffffu, clo), whi = __reduce_max_sync(0xffffffffu, chi);
+        mbar_wait(s_full + s, (u >> 1) & 1, a.status, 35);
+        tc_fence_after_sync();
+        if (u < 3) TRACE(5 + 4 * u);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tS + c * 32, rs);
-        tmem_ld32(tP + c * 32, rp);
-        tmem_ld_wait();
-        uint32_t dpk[16];
+        for (int c = 0; c < 2; ++c) {
+          const int c0 = 64 * hf + 32 * c;
+          if (c0 + 31 < wlo || c0 > whi) {   // no row of this warp sees these 32 keys
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int gk = gk0 + c * 32 + 2 * j + e;
-            const bool ok = (unsigned)(gk - gi + hw) < (unsigned)p.w && (unsigned)gk < (unsigned)len_b;
-            const float ev = ok ? ex2(fmaf(__uint_as_float(rs[2 * j + e]), sc, co)) : 0.f;
-            const float pv = ok ? __uint_as_float(rp[2 * j + e]) : 0.f;
-            L += ev;
-            dps += pv;
-            dv[e] = fmaf(-pv, psc, ev);
+            for (int j = 0; j < 16; ++j) En[16 * c + j] = 0u;
+            continue;
           }
-          dpk[j] = pack_bf16(dv[0], dv[1]);
-        }
-        tmem_st16(tD + c * 16, dpk);
-      }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(d_full + bb);
-      mbar_arrive(sp_free + bb);
-    }
-    // ---- epilogue ----
-    mbar_wait(bar_lr, 0, a.status, 31);
-    tc_fence_after_sync();
-    const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f) * psc);
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
-                          (int64_t)(i0 + tid) * p.o_stride_t;
+          uint32_t rs[32];
+          tmem_ld32(lane_base + T_BUF + s * 128 + c0, rs);
+          tmem_ld_wait();
+          const unsigned span = (unsigned)(chi - clo);
+          float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
+          for (int j = 0; j < 16; ++j) {
+            const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
+            const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
+            const float e0 = ok0 ? ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co)) : 0.f;
+            const float e1 = ok1 ? ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co)) : 0.f;
+            l0 += e0;
+            l1 += e1;
+            En[16 * c + j] = pack_bf16(e0, e1);
+          }
+          L += l0 + l1;
+        }
+        tc_fence_before_sync();
+        mbar_arrive(a_done + s);
+        if (u < 3) TRACE(6 + 4 * u);
+      }
+      if (t >= 0) {
+        // B: P(t) -> D = E - P (packed bf16 into tensor memory), row sum dps
+        const int s = t & 1;
+        int clo, chi;
+        col_range(t, clo, chi);
+        const int wlo = __reduce_min_sync(0xffffffffu, clo), whi = __reduce_max_sync(0xffffffffu, chi);
+        mbar_wait(p_full + s, (t >> 1) & 1, a.status, 36);
+        if (t >= 1) mbar_wait(d_free, (t - 1) & 1, a.status, 37);
+        tc_fence_after_sync();
+        if (t < 3) TRACE(7 + 4 * t);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int c0 = 64 * hf + 32 * c;
+          uint32_t dpk[16];
+          if (c0 + 31 < wlo || c0 > whi) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dpk[j] = 0u;
+          } else {
+            uint32_t rp[32];
+            tmem_ld32(lane_base + T_BUF + s * 128 + c0, rp);
+            tmem_ld_wait();
+            const unsigned span = (unsigned)(chi - clo);
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
+              const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
+              const float pv0 = ok0 ? __uint_as_float(rp[2 * j]) : 0.f;
+              const float pv1 = ok1 ? __uint_as_float(rp[2 * j + 1]) : 0.f;
+              d0 += pv0;
+              d1 += pv1;
+              dpk[j] = pack_bf16(bf16_lo(Ec[16 * c + j]) - pv0, bf16_hi(Ec[16 * c + j]) - pv1);
+            }
+            dps += d0 + d1;
+          }
+          tmem_st16(lane_base + T_D + 32 * hf + 16 * c, dpk);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(b_done + s);
+        if (t < 3) TRACE(8 + 4 * t);
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) Ec[j] = En[j];
+    }
+    // ---- combine the two column halves of each row ----
+    s_xch[tid] = L;
+    s_xch[256 + tid] = dps;
+    s_xch[512 + tid] = (z0 + z1) + (z2 + z3);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const int mate = tid ^ 128;
+    L += s_xch[mate];
+    dps += s_xch[256 + mate];
+    const float Z = s_xch[512 + tid] + s_xch[512 + mate];
+    // ---- epilogue: this thread writes 32 of the row's 64 outputs ----
+    mbar_wait(bar_lr, 0, a.status, 38);
+    tc_fence_after_sync();
+    TRACE(20);
+    const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
+                          (int64_t)(i0 + row) * p.o_stride_t + 32 * hf;
+    {
       // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
-      uint32_t ro[32], rl[32];
-      if (nt > 0) tmem_ld32(lane_base + T_O + c * 32, ro);
-      tmem_ld32(lane_base + T_LR + c * 32, rl);
+      uint32_t ro[32];
+      tmem_ld32(lane_base + T_O + 32 * hf, ro);
       tmem_ld_wait();
       uint32_t o[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float o0 = nt > 0 ? __uint_as_float(ro[2 * j]) : 0.f, o1 = nt > 0 ? __uint_as_float(ro[2 * j + 1]) : 0.f;
-        o[j] = pack_bf16(fmaf(psc, __uint_as_float(rl[2 * j]), o0) * inv,
-                         fmaf(psc, __uint_as_float(rl[2 * j + 1]), o1) * inv);
-      }
-      if (tid < nq) {
+      for (int j = 0; j < 16; ++j)
+        o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
+      if (row < nq) {
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          reinterpret_cast<uint4*>(orow + 32 * c)[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+          reinterpret_cast<uint4*>(orow)[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
       }
     }
   }
+  if (tid == 0) TRACE(21);
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     tmem_dealloc(tb, 512);
   }
@@ -686,6 +874,7 @@ bool map_bthe(CUtensorMap* m, const void* base, int B, int rows, int H, int64_t 
 }
 
 struct TcLayout {
+  float* wmax;
   __nv_bfloat16* wt16;
   float* wt32;
   __nv_bfloat16* phik;
@@ -702,6 +891,7 @@ TcLayout tc_layout(const SblParams& p, const Workspace& ws, char* base) {
   l.kv16 = reinterpret_cast<__nv_bfloat16*>(base + ws.qls);   // nor query log-scales
   l.partial = reinterpret_cast<float*>(base + ws.partial);
   l.status = reinterpret_cast<int*>(base + ws.status);
+  l.wmax = reinterpret_cast<float*>(base + ws.status + 16);
   (void)p;
   return l;
 }
@@ -719,6 +909,12 @@ cudaError_t launch_keys(const SblParams& p, const Workspace& ws, char* base, con
     const uint64_t str[1] = {(uint64_t)kE * 2};
     const uint32_t box[2] = {64, 128};
     if (!encode_tmap_bf16(&a.tm_w, l.wt16, 2, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)p.S, (uint64_t)(p.B * p.H)};
+    const uint64_t str[2] = {(uint64_t)kM * 2, (uint64_t)p.S * kM * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    if (!encode_tmap_bf16(&a.tm_phik, l.phik, 3, dims, str, box)) return cudaErrorInvalidValue;
   }
   a.lengths = p.key_lengths;
   a.beta_in = beta_in;
@@ -739,7 +935,7 @@ cudaError_t launch_keys(const SblParams& p, const Workspace& ws, char* base, con
                                        (int)keys::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)ws.nsplit, (unsigned)(p.B * p.H));
-  tc_keys_kernel<MAX_ONLY><<<grid, 192, keys::SMEM_BYTES, st>>>(a);
+  tc_keys_kernel<MAX_ONLY><<<grid, keys::NTHREADS, keys::SMEM_BYTES, st>>>(a);
   return cudaGetLastError();
 }
 
@@ -766,9 +962,8 @@ bool tc_supported(const SblParams& p) {
 cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
                                   bool reset_status) {
   const TcLayout l = tc_layout(p, ws, base);
-  const int n = p.r * p.E;
-  tc_prep_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(p.W, (float)sqrt((double)p.softmax_temp), l.wt32, l.wt16, n,
-                                                           l.status, reset_status ? 1 : 0);
+  tc_prep_kernel<<<1, 256, 0, st>>>(p.W, (float)sqrt((double)p.softmax_temp), l.wt32, l.wt16, p.r, p.E, l.status,
+                                    l.wmax, reset_status ? 1 : 0);
   return cudaGetLastError();
 }
 
@@ -796,8 +991,8 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   if (e != cudaSuccess) return e;
   BandArgs a{};
   if (!map_bthe(&a.tm_q, p.q, p.B, p.T, p.H, p.q_stride_b, p.q_stride_t, p.q_stride_h, 128) ||
-      !map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 64) ||
-      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 64))
+      !map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
+      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128))
     return cudaErrorInvalidValue;
   {
     const uint64_t dims[2] = {(uint64_t)kE, (uint64_t)kR};
@@ -808,7 +1003,7 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   {
     const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)p.S, (uint64_t)(p.B * p.H)};
     const uint64_t str[2] = {(uint64_t)kM * 2, (uint64_t)p.S * kM * 2};
-    const uint32_t box[3] = {64, 64, 1};
+    const uint32_t box[3] = {64, 128, 1};
     if (!encode_tmap_bf16(&a.tm_phik, l.phik, 3, dims, str, box)) return cudaErrorInvalidValue;
   }
   {
@@ -820,13 +1015,23 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   a.p = p;
   a.beta = beta;
   a.ksum = ksum;
+  a.wmax = l.wmax;
   a.status = l.status;
   e = cudaFuncSetAttribute(tc_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)div_up(p.T, band::BQ), (unsigned)(p.B * p.H));
-  tc_band_kernel<<<grid, 192, band::SMEM_BYTES, st>>>(a);
+  tc_band_kernel<<<grid, band::NTHREADS, band::SMEM_BYTES, st>>>(a);
   return cudaGetLastError();
 }
+
+#ifdef SBL_TRACE
+extern "C" int sbl_trace_fetch(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * 64 * 32);
+}
+extern "C" int sbl_trace_fetch2(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace2, sizeof(long long) * 64 * 2 * 32);
+}
+#endif
 
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st) {
   cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, sizeof(int), cudaMemcpyDeviceToHost, st);
