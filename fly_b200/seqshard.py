@@ -1,0 +1,139 @@
+"""Sequence-sharded SBLocal forward: one long sequence split along N over the
+ranks of a torch.distributed group (one process per GPU, NCCL over NVLink).
+
+The reference has no sequence parallelism; the decomposition is exact because
+the only couplings between tokens are (i) the band, served by a halo of
+w//2 keys before and w-1-w//2 keys after the shard, and (ii) three global
+reductions: the key log-scale beta (max), phi(K)^T V and sum phi(K) (sums),
+cf. src/models/attention/sblocal_attention.py:87-97 and
+src/models/attention/feature_maps_sb.py:78.
+
+Protocol per forward (rank g owns rows [lo, hi) of q, k, v, out):
+  1. halo exchange: every rank sends the K/V rows other ranks' windows reach
+     into (point-to-point, into the receivers' own memory);
+  2. sbl_key_logscale over the own rows        -> all-reduce MAX of (B,H) floats;
+  3. sbl_key_summary over own rows (+phi(K) of the halo rows kept in the
+     workspace)                                -> all-reduce SUM of (B,H,m,D+1) floats;
+  4. sbl_band_forward over the local queries, reading local memory only.
+No kernel ever touches another GPU's memory.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n_total, world):
+    """Contiguous, near-equal shards: rank g owns [b[g], b[g+1])."""
+    return [n_total * g // world for g in range(world + 1)]
+
+
+def halo_range(lo, hi, w, n_total):
+    """Global key rows [klo, khi) the queries [lo, hi) can see."""
+    return max(0, lo - w // 2), min(n_total, hi - 1 - w // 2 + w)
+
+
+def plan_halo(bounds, w, rank):
+    """Returns (sends, recvs): lists of (peer, global_lo, global_hi) row ranges
+    this rank must send to / receive from each peer."""
+    world = len(bounds) - 1
+    n_total = bounds[-1]
+    lo, hi = bounds[rank], bounds[rank + 1]
+    klo, khi = halo_range(lo, hi, w, n_total)
+    recvs, sends = [], []
+    for peer in range(world):
+        if peer == rank:
+            continue
+        plo, phi = bounds[peer], bounds[peer + 1]
+        a, b = max(klo, plo), min(khi, phi)          # rows of the peer inside my halo
+        if a < b and hi > lo:
+            recvs.append((peer, a, b))
+        pklo, pkhi = halo_range(plo, phi, w, n_total)
+        a, b = max(pklo, lo), min(pkhi, hi)          # my rows inside the peer's halo
+        if a < b and phi > plo:
+            sends.append((peer, a, b))
+    return sends, recvs
+
+
+def exchange_halo(k_local, v_local, bounds, w, group=None):
+    """Returns (k_ext, v_ext, klo): the local K/V rows extended by the halo
+    rows received from the neighbours, and the global position of row 0."""
+    rank = dist.get_rank(group)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    n_total = bounds[-1]
+    klo, khi = halo_range(lo, hi, w, n_total)
+    sends, recvs = plan_halo(bounds, w, rank)
+    B, _, H, E = k_local.shape
+    D = v_local.shape[-1]
+    k_ext = k_local.new_empty(B, khi - klo, H, E)
+    v_ext = v_local.new_empty(B, khi - klo, H, D)
+    k_ext[:, lo - klo:hi - klo] = k_local
+    v_ext[:, lo - klo:hi - klo] = v_local
+    ops_, keep = [], []
+    for peer, a, b in sends:
+        ks = k_local[:, a - lo:b - lo].contiguous()
+        vs = v_local[:, a - lo:b - lo].contiguous()
+        keep += [ks, vs]
+        ops_ += [dist.P2POp(dist.isend, ks, _global_rank(peer, group), group),
+                 dist.P2POp(dist.isend, vs, _global_rank(peer, group), group)]
+    landing = []
+    for peer, a, b in recvs:
+        kr = k_local.new_empty(B, b - a, H, E)
+        vr = v_local.new_empty(B, b - a, H, D)
+        landing.append((a, b, kr, vr))
+        ops_ += [dist.P2POp(dist.irecv, kr, _global_rank(peer, group), group),
+                 dist.P2POp(dist.irecv, vr, _global_rank(peer, group), group)]
+    if ops_:
+        for req in dist.batch_isend_irecv(ops_):
+            req.wait()
+    for a, b, kr, vr in landing:
+        k_ext[:, a - klo:b - klo] = kr
+        v_ext[:, a - klo:b - klo] = vr
+    return k_ext, v_ext, klo
+
+
+def _global_rank(group_rank, group):
+    return group_rank if group is None else dist.get_global_rank(group, group_rank)
+
+
+class CudaEngine:
+    """The three stage calls of the C ABI on this rank's shard."""
+
+    def __init__(self, q_local, k_ext, v_ext, W, w, tau, eps, key_lengths, lo, klo, n_total, n_own):
+        from . import ops
+        self.prob = ops.Problem(q_local, k_ext, v_ext, W, w, tau, eps, key_lengths,
+                                q_pos0=lo, k_pos0=klo, S_total=n_total,
+                                sum_range=(lo - klo, lo - klo + n_own))
+        self.ws = self.prob.workspace()
+
+    def key_logscale(self):
+        return self.prob.key_logscale(workspace=self.ws)
+
+    def key_summary(self, beta):
+        return self.prob.key_summary(beta, workspace=self.ws)
+
+    def band_forward(self, beta, kv, ksum):
+        return self.prob.band_forward(beta, kv, ksum, workspace=self.ws)
+
+
+def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_total, softmax_temp=None,
+                             softmax_eps=0.0, key_lengths=None, group=None, engine_cls=CudaEngine):
+    """SBLocal forward of this rank's shard of one long sequence.
+
+    q_local/k_local/v_local: (B, n_local, H, E|D), rows
+    shard_bounds(n_total, world)[rank] ... [rank+1] of the full sequence.
+    key_lengths: global (B,) key lengths or None.  Returns out (B, n_local, H, D).
+    """
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    bounds = shard_bounds(n_total, world)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    if q_local.shape[1] != hi - lo or k_local.shape[1] != hi - lo or v_local.shape[1] != hi - lo:
+        raise ValueError(f'rank {rank} must hold rows [{lo},{hi}) of the sequence: got {q_local.shape[1]} rows')
+    k_ext, v_ext, klo = exchange_halo(k_local, v_local, bounds, int(local_context), group)
+    eng = engine_cls(q_local, k_ext, v_ext, W, int(local_context), softmax_temp, softmax_eps, key_lengths,
+                     lo, klo, n_total, hi - lo)
+    beta = eng.key_logscale()
+    dist.all_reduce(beta, op=dist.ReduceOp.MAX, group=group)
+    kv, ksum = eng.key_summary(beta)
+    packed = torch.cat([kv, ksum.unsqueeze(-1)], dim=-1).contiguous()     # one collective for both
+    dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+    kv, ksum = packed[..., :-1].contiguous(), packed[..., -1].contiguous()
+    return eng.band_forward(beta, kv, ksum)
