@@ -66,25 +66,27 @@ __device__ __forceinline__ float row_sumsq_sw128(const uint8_t* tile, int row) {
 }
 
 // ---------------------------------------------------------------------------
-// One block: sqrt(tau)*W in fp32 and bf16, the largest row norm of the bf16
-// copy (bound on |u_f| / |x| used as the query feature stabiliser), status reset.
-__global__ void __launch_bounds__(256) tc_prep_kernel(const float* W, float c, float* wt32, __nv_bfloat16* wt16, int r,
-                                                      int E, int* status, float* wmax, int reset_status) {
-  __shared__ float red[8];
-  const int n = r * E;
-  for (int i = threadIdx.x; i < n; i += 256) {
-    const float v = c * W[i];
-    wt32[i] = v;
-    wt16[i] = __float2bfloat16_rn(v);
-  }
-  __syncthreads();
+// One block of 1024 threads, 8 per projection row: sqrt(tau)*W in fp32 and bf16, the largest row
+// norm of the bf16 copy (bound on |u_f| / |x| used as the query feature stabiliser), status reset.
+__global__ void __launch_bounds__(1024) tc_prep_kernel(const float* W, float c, float* wt32, __nv_bfloat16* wt16,
+                                                       int r, int E, int* status, float* wmax, int reset_status) {
+  __shared__ float red[32];
   float mx = 0.f;
-  for (int f = threadIdx.x; f < r; f += 256) {
+  for (int f0 = 0; f0 < r; f0 += 128) {
+    const int f = f0 + threadIdx.x / 8, part = threadIdx.x % 8;
     float s = 0.f;
-    for (int e = 0; e < E; ++e) {
-      const float v = __bfloat162float(wt16[f * E + e]);
-      s = fmaf(v, v, s);
-    }
+    if (f < r)
+      for (int e = part; e < E; e += 8) {
+        const float v = c * W[f * E + e];
+        const __nv_bfloat16 b = __float2bfloat16_rn(v);
+        wt32[f * E + e] = v;
+        wt16[f * E + e] = b;
+        const float vb = __bfloat162float(b);
+        s = fmaf(vb, vb, s);
+      }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
     mx = fmaxf(mx, s);
   }
 #pragma unroll
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(256) tc_prep_kernel(const float* W, float c, f
   if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = mx;
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+    for (int i = 1; i < 32; ++i) mx = fmaxf(mx, red[i]);
     *wmax = sqrtf(mx) * 1.0005f;
   }
   if (reset_status && threadIdx.x < 4) status[threadIdx.x] = 0;
@@ -195,7 +197,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tb = *tmem_slot;
+  constexpr uint32_t tb = 0;   // the CTA owns all 512 tensor-memory columns of its SM
+  if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 41);
 
   // a tile whose rows all enter the summary and hold real keys is stored to the workspace by one bulk copy
   auto tile_is_plain = [&](int i) {
@@ -441,7 +444,7 @@ constexpr uint32_t T_PHIQ = 0;     // 128: phi(Q) packed bf16 (256 features)
 constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, later P of the same tile
 constexpr uint32_t T_O = 384;      // 64
 constexpr uint32_t T_D = 448;      // 64: D packed bf16 (128 keys)
-constexpr uint32_t T_UQ = 128;     // aliases buffer 0 before the band loop
+constexpr uint32_t T_UQ = 256;     // aliases buffer 1 before the band loop
 }  // namespace band
 
 __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_constant__ BandArgs a) {
@@ -484,24 +487,12 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   const int j0 = (lo / KT) * KT;
   const int nt = hi >= lo ? (hi - j0) / KT + 1 : 0;
 
-  if (tid == 0) {
-    mbar_init(bar_qw, 1);
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_uq, 1);
-    mbar_init(bar_phiq, NSOFT);
-    mbar_init(bar_lr, 1);
-    mbar_init(d_free, 1);
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(pk_full + i, 1);
-      mbar_init(pk_empty + i, 1);
-      mbar_init(s_full + i, 1);
-      mbar_init(a_done + i, NSOFT);
-      mbar_init(p_full + i, 1);
-      mbar_init(b_done + i, NSOFT);
+  if (tid == 0) TRACE(0);
+  if (warp == 9) {
+    // one barrier per lane; arrival counts: the softmax-side barriers take NSOFT arrivals, the rest one
+    if (lane < 34) {
+      const bool soft = lane == 3 || lane == 16 || lane == 17 || lane == 20 || lane == 21;
+      mbar_init(bars + lane, soft ? NSOFT : 1);
     }
     fence_mbar_init();
   }
@@ -509,12 +500,13 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (tid == 0) TRACE(0);
-  for (int i = tid; i < kM; i += NTHREADS) s_ksum[i] = a.ksum[(int64_t)bh * kM + i];
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tb = *tmem_slot;
+  // The CTA owns all 512 columns of its SM's tensor memory, so the allocation starts at
+  // column 0; keeping the base a compile-time constant keeps every MMA operand uniform.
+  constexpr uint32_t tb = 0;
+  if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 40);
   if (tid == 0) TRACE(1);
 
   if (warp == 8) {
@@ -647,9 +639,9 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       mma_commit(bar_uq);
     }
     __syncwarp();
+    if (nt > 0) issue_s(0);          // S(0) does not need phi(Q): it runs while the softmax warps form it
     mbar_wait(bar_phiq, 0, a.status, 31);
     tc_fence_after_sync();
-    if (nt > 0) issue_s(0);
     if (nt > 1) issue_s(1);
     // O starts as the low-rank numerator phi(Q) KV; the band tiles accumulate onto it
     mbar_wait(bar_kv, 0, a.status, 32);
@@ -683,6 +675,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     const int row = qd * 32 + lane;                  // query row of this thread
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
     const int gi = (int)p.q_pos0 + i0 + row;         // global query position
+    for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)bh * kM + i];
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     // ---- phi(Q): this thread's 64 projections -> 128 features ----
     mbar_wait(bar_qw, 0, a.status, 33);
     const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
@@ -962,7 +956,7 @@ bool tc_supported(const SblParams& p) {
 cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
                                   bool reset_status) {
   const TcLayout l = tc_layout(p, ws, base);
-  tc_prep_kernel<<<1, 256, 0, st>>>(p.W, (float)sqrt((double)p.softmax_temp), l.wt32, l.wt16, p.r, p.E, l.status,
+  tc_prep_kernel<<<1, 1024, 0, st>>>(p.W, (float)sqrt((double)p.softmax_temp), l.wt32, l.wt16, p.r, p.E, l.status,
                                     l.wmax, reset_status ? 1 : 0);
   return cudaGetLastError();
 }

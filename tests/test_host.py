@@ -96,3 +96,16 @@ def test_masks():
 def test_package_exports():
     for name in ('SBLocalAttention', 'SBPerformerFeatures', 'gaussian_orthogonal_random_matrix', 'LengthMask'):
         assert hasattr(fly_b200, name)
+
+
+def test_dropin_registers_the_reference_module_path():
+    import importlib
+    from fly_b200 import dropin
+    dropin.install()
+    mod = importlib.import_module('src.models.attention.sblocal_attention')
+    assert mod.SBLocalAttention is SBLocalAttention
+    # what hydra.utils.instantiate does with a _target_ string: locate, then call with the config's kwargs
+    path, _, name = 'src.models.attention.sblocal_attention.SBLocalAttention'.rpartition('.')
+    cls = getattr(importlib.import_module(path), name)
+    layer = cls(dim_heads=64, local_context=49, nb_features=24, softmax_temp=147 ** -0.5)
+    assert isinstance(layer, SBLocalAttention) and layer.feature_map.n_features == 24
