@@ -238,13 +238,20 @@ def main():
     torch.cuda.synchronize(dev)
     nb = max(5, min(args.steps, 20))
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nb)]
-    for a, b in evs:
-        prob.key_summary(beta)          # evicts the band kernel's inputs from L2 between repeats
+    stage_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(nb)]
+    for (a, b), se in zip(evs, stage_ev):
+        se[0].record()
+        prob.key_logscale()
+        se[1].record()
+        prob.key_summary(beta)          # also evicts the band kernel's inputs from L2 between repeats
+        se[2].record()
         a.record()
         prob.band_forward(beta, kv, ksum)
         b.record()
     torch.cuda.synchronize(dev)
     band_ms = sum(a.elapsed_time(b) for a, b in evs) / nb
+    logscale_ms = sum(se[0].elapsed_time(se[1]) for se in stage_ev) / nb
+    summary_ms = sum(se[1].elapsed_time(se[2]) for se in stage_ev) / nb
 
     # ---- end to end through the module: host buffers in, host buffer out ----
     layer = SBLocalAttention(w, d, m).to(dev).eval()
@@ -304,6 +311,7 @@ def main():
             roofline=dict(bound='tensor', kernel='band', achieved=achieved, peak=peak_tf, unit='TFLOP/s',
                           frac=achieved / peak_tf, traffic=None, peak_source=peaks['source'],
                           kernel_ms=band_ms),
+            stage_ms=dict(key_logscale=logscale_ms, key_summary=summary_ms, band_forward=band_ms),
             roofline_forward=dict(bound='tensor', achieved=fwd_flops / (ms_per_step * 1e-3) / 1e12, peak=peak_tf,
                                   unit='TFLOP/s', frac=fwd_flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
                                   hbm_gbs=4 * th * d * elem / (ms_per_step * 1e-3) / 1e9,

@@ -117,7 +117,7 @@ bool plan_workspace(const SblParams& p, Workspace* ws, const char** why) {
   ws->beta = off;    off = align_up(off + BH * 4);
   ws->kv = off;      off = align_up(off + BH * m * p.D * 4);
   ws->ksum = off;    off = align_up(off + BH * m * 4);
-  ws->partial = off; off = align_up(off + BH * ws->nsplit * m * (p.D + 1) * 4);
+  ws->partial = off; off = align_up(off + BH * ws->nsplit * m * (ws->tensor ? 80 : p.D + 1) * 4);
   ws->status = off;  off = align_up(off + 64);
   ws->total = off;
   (void)why;

@@ -34,6 +34,7 @@ constexpr int kE = 64;    // head dim (qk and v)
 constexpr int kR = 128;   // projection rows
 constexpr int kM = 256;   // features
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kPartialLd = 80;   // row pitch (floats) of a split-partial summary: 64 KV columns, the feature sum, padding
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -100,12 +101,39 @@ __global__ void __launch_bounds__(1024) tc_prep_kernel(const float* W, float c, 
   if (reset_status && threadIdx.x < 4) status[threadIdx.x] = 0;
 }
 
+// kv (BH,256,64), ksum (BH,256) = sum over the splits of the per-CTA partial summaries
+__global__ void tc_combine_kernel(const float* partial, int nsplit, int BH, float* kv, float* ksum) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over BH * 256 * 20 float4 groups
+  if (i >= (int64_t)BH * kM * (kPartialLd / 4)) return;
+  const int g = (int)(i % (kPartialLd / 4));
+  const int64_t bf = i / (kPartialLd / 4);        // bh * 256 + f
+  if (g > 16) return;
+  const int64_t bh = bf / kM, f = bf % kM;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = 0; k < nsplit; ++k) {
+    const float4 v = *reinterpret_cast<const float4*>(partial + ((bh * nsplit + k) * kM + f) * kPartialLd + 4 * g);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (g < 16) *reinterpret_cast<float4*>(kv + bf * kE + 4 * g) = acc;
+  else ksum[bf] = acc.x;
+}
+
 __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) kv16[i] = __float2bfloat16_rn(kv[i]);
 }
 
 // ---------------------------------------------------------------------------
+#ifdef SBL_TRACE
+__device__ long long g_trace[64][32];
+__device__ long long g_trace2[64][2][32];   // [cta][0 = producer, 1 = MMA issuer][slot]
+#define TRACE(slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (threadIdx.x == 0)) g_trace[blockIdx.y * 8 + blockIdx.x][slot] = clock64(); } while (0)
+#define TRACE2(who, slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (slot) < 32) g_trace2[blockIdx.y * 8 + blockIdx.x][who][slot] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#define TRACE2(who, slot) do { } while (0)
+#endif
+
 // keys kernel
 struct KeysArgs {
   CUtensorMap tm_k, tm_v, tm_w, tm_phik;
@@ -125,10 +153,10 @@ constexpr int TILE = 128;
 constexpr int NFEAT = 256;                 // feature threads: warps 0-7; warp w owns key rows 32*(w%4).., projection half w/4
 constexpr int NTHREADS = NFEAT + 64;       // + producer warp 8 + MMA warp 9
 constexpr uint32_t OFF_W = 0;                    // 16 KB  [128 r][64 e]
-constexpr uint32_t OFF_STAGE = 16384;            // 2 x { K 16 KB, V 16 KB, ones 16 KB }: [V | 1] is one MN-major operand, N = 80
-constexpr uint32_t STAGE_BYTES = 49152;
-constexpr uint32_t OFF_A = OFF_STAGE + 2 * STAGE_BYTES;  // 64 KB: 4 blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
-constexpr uint32_t OFF_BAR = OFF_A + 65536;
+constexpr uint32_t OFF_K = 16384;                // ring of [128 keys][64 e] tiles, 16 KB each: 2 deep (4 deep in the beta pass)
+constexpr uint32_t OFF_V = 49152;                // { V 16 KB, ones 16 KB }: [V | 1] is one MN-major operand, N = 80
+constexpr uint32_t OFF_A = OFF_V + 32768;        // 2 x 64 KB: 4 blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
+constexpr uint32_t OFF_BAR = OFF_A + 2 * 65536;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;    // + alignment slack
 // tensor memory columns
 constexpr uint32_t T_UK = 0;      // 2 x 128
@@ -142,7 +170,7 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
                : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <bool MAX_ONLY>
@@ -153,14 +181,17 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint64_t* bar_w = bars + 0;
   uint64_t* bar_done = bars + 1;
-  uint64_t* full = bars + 2;      // [2] K (and V) tile landed
-  uint64_t* empty = bars + 4;     // [2] stage may be refilled
-  uint64_t* uk_full = bars + 6;   // [2] U = K Wt^T computed
-  uint64_t* uk_free = bars + 8;   // [2] U read by all feature threads
-  uint64_t* a_full = bars + 10;   // phi(K) tile written to shared memory
-  uint64_t* a_free = bars + 11;   // phi(K) tile consumed (MMA done + bulk store has read it)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  float* red = reinterpret_cast<float*>(bars + 13);  // [8]
+  uint64_t* v_full = bars + 2;    // V tile landed (single buffer, one completion per tile)
+  uint64_t* v_empty = bars + 3;   // V tile consumed by the summary MMAs
+  uint64_t* k_full = bars + 4;    // [KD] K tile landed
+  uint64_t* k_free = bars + 8;    // [KD] K tile consumed: U computed and every row norm read
+  uint64_t* uk_full = bars + 12;  // [2] U = K Wt^T computed
+  uint64_t* uk_free = bars + 14;  // [2] U read by all feature threads
+  uint64_t* a_full = bars + 16;   // [2] phi(K) tile written to shared memory
+  uint64_t* a_free = bars + 18;   // [2] phi(K) tile consumed (MMAs done + bulk store has read it)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  float* red = reinterpret_cast<float*>(bars + 21);  // [8]
+  constexpr int KD = MAX_ONLY ? 4 : 2;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
@@ -170,18 +201,23 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   const int t_hi = (int)((int64_t)ntiles * (split + 1) / a.nsplit);
   const int nt = t_hi - t_lo;
   const int64_t len_b = a.lengths ? min(a.lengths[b], a.S_total) : a.S_total;
+  if (!MAX_ONLY && tid == 0) TRACE(0);
 
   if (tid == 0) {
     mbar_init(bar_w, 1);
     mbar_init(bar_done, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(k_full + i, 1);
+      mbar_init(k_free + i, NFEAT);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(full + i, 1);
-      mbar_init(empty + i, 1);
       mbar_init(uk_full + i, 1);
       mbar_init(uk_free + i, NFEAT);
+      mbar_init(a_full + i, NFEAT);
+      mbar_init(a_free + i, 2);
     }
-    mbar_init(a_full, NFEAT);
-    mbar_init(a_free, 2);
     fence_mbar_init();
   }
   if (warp == 8) {
@@ -189,10 +225,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     tmem_relinquish();
   }
   if (!MAX_ONLY)
-    for (int i = tid; i < 2 * 8192; i += NTHREADS) {   // the "ones" block of both stages (16 KB each, bf16 1.0)
-      const int s = i / 8192, j = i % 8192;
-      reinterpret_cast<__nv_bfloat16*>(smem + OFF_STAGE + s * STAGE_BYTES + 32768)[j] = __float2bfloat16(1.0f);
-    }
+    for (int i = tid; i < 8192; i += NTHREADS)   // the "ones" block behind the V tile (16 KB of bf16 1.0)
+      reinterpret_cast<__nv_bfloat16*>(smem + OFF_V + 16384)[i] = __float2bfloat16(1.0f);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -218,14 +252,27 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       tma_load_2d(smem + OFF_W, &a.tm_w, bar_w, 0, 0);
     }
     for (int i = 0; i < nt; ++i) {
-      const int s = i & 1;
-      if (i >= 2) mbar_wait(empty + s, ((i >> 1) - 1) & 1, a.status, 11);
+      const int ks = i % KD;
+      const int row0 = (t_lo + i) * TILE;
+      if (i >= KD) mbar_wait(k_free + ks, ((i / KD) - 1) & 1, a.status, 11);
       if (leader) {
-        uint8_t* st = smem + OFF_STAGE + s * STAGE_BYTES;
-        const int row0 = (t_lo + i) * TILE;
-        mbar_expect_tx(full + s, MAX_ONLY ? 16384 : 32768);
-        tma_load_4d(st, &a.tm_k, full + s, 0, row0, h, b);
-        if (!MAX_ONLY) tma_load_4d(st + 16384, &a.tm_v, full + s, 0, row0, h, b);
+        mbar_expect_tx(k_full + ks, 16384);
+        tma_load_4d(smem + OFF_K + ks * 16384, &a.tm_k, k_full + ks, 0, row0, h, b);
+      }
+      if (!MAX_ONLY && i >= 1) {
+        // V(i-1): single buffer, free once the summary MMAs of tile i-2 are done; it is needed well after K(i)
+        if (i >= 2) mbar_wait(v_empty, (i - 2) & 1, a.status, 11);
+        if (leader) {
+          mbar_expect_tx(v_full, 16384);
+          tma_load_4d(smem + OFF_V, &a.tm_v, v_full, 0, row0 - TILE, h, b);
+        }
+      }
+    }
+    if (!MAX_ONLY && nt >= 1) {
+      if (nt >= 2) mbar_wait(v_empty, (nt - 2) & 1, a.status, 11);
+      if (leader) {
+        mbar_expect_tx(v_full, 16384);
+        tma_load_4d(smem + OFF_V, &a.tm_v, v_full, 0, (t_lo + nt - 1) * TILE, h, b);
       }
     }
     __syncwarp();
@@ -235,44 +282,51 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     constexpr uint32_t id_uk = idesc_bf16(128, 128, false, false);
     constexpr uint32_t id_kv = idesc_bf16(128, 80, true, true);
     const uint64_t dW = smem_desc_sw128(smem_u32(smem + OFF_W), 16, 1024);
-    const uint64_t dA = smem_desc_sw128(smem_u32(smem + OFF_A), 16384, 1024);
-    const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_STAGE), 16, 1024);
-    const uint64_t dV0 = smem_desc_sw128(smem_u32(smem + OFF_STAGE + 16384), 16384, 1024);  // second MN block = ones
+    const uint64_t dA0 = smem_desc_sw128(smem_u32(smem + OFF_A), 16384, 1024);
+    const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_K), 16, 1024);
+    const uint64_t dV = smem_desc_sw128(smem_u32(smem + OFF_V), 16384, 1024);  // second MN block = ones
     auto issue_kv = [&](int u) {
       const int s = u & 1;
-      mbar_wait(a_full, u & 1, a.status, 12);
+      mbar_wait(a_full + s, (u >> 1) & 1, a.status, 12);
+      mbar_wait(v_full, u & 1, a.status, 14);
       tc_fence_after_sync();
       if (leader) {
-        const bool plain = tile_is_plain(u);
-        if (plain) {
+        if (!MAX_ONLY) TRACE2(1, 2 * u);
+        // bulk copy of the phi(K) tile to the workspace (an empty group keeps the group count uniform)
+        if (tile_is_plain(u)) {
           const int row0 = (t_lo + u) * TILE;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) tma_store_3d(&a.tm_phik, smem + OFF_A + j * 16384, j * 64, row0, bh);
-          tma_store_commit();
+          for (int j = 0; j < 4; ++j)
+            tma_store_3d(&a.tm_phik, smem + OFF_A + s * 65536 + j * 16384, j * 64, row0, bh);
         }
-        const uint64_t dV = dV0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+        tma_store_commit();
+        const uint64_t dA = dA0 + (uint64_t)(s * (65536 >> 4));
 #pragma unroll
         for (int mb = 0; mb < 2; ++mb)
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             mma_ss(tb + T_KV + mb * 128, dA + (uint64_t)(mb * (32768 >> 4) + k * (2048 >> 4)),
                    dV + (uint64_t)(k * (2048 >> 4)), id_kv, (u > 0) || (k > 0));
-        mma_commit(a_free);
-        mma_commit(empty + s);
-        if (plain) tma_store_wait_read();
-        mbar_arrive(a_free);
+        mma_commit(a_free + s);
+        mma_commit(v_empty);
+        // the previous tile's bulk copy has read its buffer once at most one group is pending
+        if (u >= 1) {
+          tma_store_wait_read1();
+          mbar_arrive(a_free + (s ^ 1));
+        }
+        if (!MAX_ONLY) TRACE2(1, 2 * u + 1);
       }
       __syncwarp();
     };
     mbar_wait(bar_w, 0, a.status, 13);
     for (int i = 0; i < nt; ++i) {
       const int s = i & 1;
-      mbar_wait(full + s, (i >> 1) & 1, a.status, 14);
+      mbar_wait(k_full + (i % KD), (i / KD) & 1, a.status, 14);
       if (i >= 2) mbar_wait(uk_free + s, ((i >> 1) - 1) & 1, a.status, 15);
       tc_fence_after_sync();
       if (leader) {
-        const uint64_t dK = dK0 + (uint64_t)(s * (STAGE_BYTES >> 4));
         const uint32_t td = tb + T_UK + s * 128;
+        const uint64_t dK = dK0 + (uint64_t)((i % KD) * (16384 >> 4));
         mma_ss(td, dK, dW, id_uk, false);
         mma_ss(td, dK + 2, dW + 2, id_uk, true);
         mma_ss(td, dK + 4, dW + 4, id_uk, true);
@@ -298,11 +352,12 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     for (int i = 0; i < nt; ++i) {
       const int s = i & 1;
       const int row = (t_lo + i) * TILE + krow;
-      mbar_wait(full + s, (i >> 1) & 1, a.status, 19);
-      const uint8_t* sK = smem + OFF_STAGE + s * STAGE_BYTES;
-      const float g = 0.5f * a.tau * row_sumsq_sw128(sK, krow);
-      mbar_wait(uk_full + s, (i >> 1) & 1, a.status, 16);
+      mbar_wait(k_full + (i % KD), (i / KD) & 1, a.status, 19);
+      const float g = 0.5f * a.tau * row_sumsq_sw128(smem + OFF_K + (i % KD) * 16384, krow);
+      mbar_wait(uk_full + s, (i >> 1) & 1, a.status, 16);   // U computed: the tensor core is done with the K tile too
       tc_fence_after_sync();
+      mbar_arrive(k_free + (i % KD));
+      if (!MAX_ONLY && i < 9) TRACE(1 + 3 * i);
       if (MAX_ONLY) {
         float mx = 0.f;
 #pragma unroll
@@ -316,18 +371,13 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         if (row >= a.sum_lo && row < a.sum_hi) run_max = fmaxf(run_max, (mx - g) - a.half_log_m);
         tc_fence_before_sync();
         mbar_arrive(uk_free + s);
-        // MAX mode has no summary MMA to release the stage: the last reader does
-        if (i + 2 < nt) {
-          asm volatile("bar.sync 1, 256;" ::: "memory");   // every row has read its K row and its U values
-          if (tid == 0) mbar_arrive(empty + s);
-        }
       } else {
         const bool live = row < a.S && (a.k_pos0 + row) < len_b;
         const bool in_sum = live && row >= a.sum_lo && row < a.sum_hi;
         const bool plain = tile_is_plain(i);
         const float off = ((-g - a.half_log_m) - beta) * kLog2e;
         __nv_bfloat16* grow = a.phik + ((int64_t)bh * a.S + row) * kM;
-        uint8_t* sA = smem + OFF_A;
+        uint8_t* sA = smem + OFF_A + s * 65536;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int f0 = 64 * hf + 32 * c;           // first projection of this chunk
@@ -350,7 +400,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
             }
           }
           // the previous tile's MMAs and bulk store must be done with the shared phi(K) buffer
-          if (c == 0 && i >= 1) mbar_wait(a_free, (i - 1) & 1, a.status, 17);
+          if (c == 0 && i >= 2) mbar_wait(a_free + s, ((i >> 1) - 1) & 1, a.status, 17);
+          if (c == 0 && i < 9) TRACE(2 + 3 * i);
           // MN-major A operand: block = feature / 64, 16-byte chunk = (feature % 64) / 8, swizzled by key % 8
           const int blk = f0 >> 6;                   // = hf
 #pragma unroll
@@ -366,8 +417,9 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         }
         fence_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(a_full);
+        mbar_arrive(a_full + s);
         mbar_arrive(uk_free + s);
+        if (i < 9) TRACE(3 + 3 * i);
       }
     }
     if (MAX_ONLY) {
@@ -383,21 +435,29 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     } else {
       mbar_wait(bar_done, 0, a.status, 18);
       tc_fence_after_sync();
+      TRACE(30);
       // thread (feature row, half): half 0 writes KV columns 0-31, half 1 columns 32-63 and the feature sum
-      float* part = a.partial + ((int64_t)bh * a.nsplit + split) * kM * 65;
+      float* part = a.partial + ((int64_t)bh * a.nsplit + split) * kM * kPartialLd;
 #pragma unroll
       for (int mb = 0; mb < 2; ++mb) {
-        float* prow = part + (int64_t)(mb * 128 + krow) * 65;
+        float* prow = part + (int64_t)(mb * 128 + krow) * kPartialLd;
         uint32_t r[32], q[16];
         tmem_ld32(lane_base + T_KV + mb * 128 + 32 * hf, r);
         tmem_ld16(lane_base + T_KV + mb * 128 + 64, q);
         tmem_ld_wait();
+        if (nt == 0) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) prow[32 * hf + j] = nt > 0 ? __uint_as_float(r[j]) : 0.f;
-        if (hf == 1) prow[64] = nt > 0 ? __uint_as_float(q[0]) : 0.f;
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+          q[0] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          reinterpret_cast<uint4*>(prow + 32 * hf)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        if (hf == 1) prow[64] = __uint_as_float(q[0]);
       }
     }
   }
+  if (!MAX_ONLY && tid == 0) TRACE(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 8) {
@@ -417,20 +477,11 @@ struct BandArgs {
   int* status;
 };
 
-#ifdef SBL_TRACE
-__device__ long long g_trace[64][32];
-__device__ long long g_trace2[64][2][32];   // [cta][0 = producer, 1 = MMA issuer][slot]
-#define TRACE(slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (tid == 0)) g_trace[blockIdx.y * 8 + blockIdx.x][slot] = clock64(); } while (0)
-#define TRACE2(who, slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (slot) < 32) g_trace2[blockIdx.y * 8 + blockIdx.x][who][slot] = clock64(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#define TRACE2(who, slot) do { } while (0)
-#endif
 
 namespace band {
 constexpr int BQ = 128, KT = 128;
 constexpr int NSOFT = 256;                 // softmax threads: warps 0-7; warp w owns rows 32*(w%4).., column half w/4
-constexpr int NTHREADS = NSOFT + 64;       // + producer warp 8 + MMA warp 9
+constexpr int NTHREADS = NSOFT + 96;       // + producer warp 8 + MMA warps 9 (S, O, low-rank) and 10 (P)
 constexpr uint32_t OFF_Q = 0;              // 16 KB [128 q][64 e]
 constexpr uint32_t OFF_KV = 16384;         // 32 KB [256 f][64 d]; its first 16 KB hold Wt [128 r][64 e] until U is computed
 constexpr uint32_t OFF_K = 49152;          // 16 KB [128 keys][64 e]
@@ -596,23 +647,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       }
       __syncwarp();
     };
-    auto issue_p = [&](int t) {
-      const int s = t & 1;
-      mbar_wait(a_done + s, (t >> 1) & 1, a.status, 26);
-      mbar_wait(pk_full + s, (t >> 1) & 1, a.status, 27);
-      tc_fence_after_sync();
-      if (leader) {
-        TRACE2(1, 2 + 8 * t);
-        const uint64_t dPK = dPK0 + (uint64_t)(s * (65536 >> 4));
-        const uint32_t td = tb + T_BUF + s * 128;
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-          mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
-        mma_commit(pk_empty + s);
-        mma_commit(p_full + s);
-      }
-      __syncwarp();
-    };
     auto issue_o = [&](int u) {
       const int s = u & 1;
       mbar_wait(b_done + s, (u >> 1) & 1, a.status, 28);
@@ -652,16 +686,13 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         mma_ts(tb + T_O, tb + T_PHIQ + k * 8, dKV + (uint64_t)(k * (2048 >> 4)), id_o, k > 0);
     }
     __syncwarp();
-    for (int t = 0; t < nt; ++t) {
-      issue_p(t);
-      if (t >= 1) {
-        // both need B(t-1) finished; S first, the softmax warps are waiting for it
-        if (t + 1 < nt) {
-          mbar_wait(b_done + ((t - 1) & 1), ((t - 1) >> 1) & 1, a.status, 28);
-          issue_s(t + 1);
-        }
-        issue_o(t - 1);
+    for (int t = 1; t < nt; ++t) {
+      // both need B(t-1) finished; S first, the softmax warps are waiting for it
+      if (t + 1 < nt) {
+        mbar_wait(b_done + ((t - 1) & 1), ((t - 1) >> 1) & 1, a.status, 28);
+        issue_s(t + 1);
       }
+      issue_o(t - 1);
     }
     if (nt > 0) issue_o(nt - 1);
     if (leader) {
@@ -669,6 +700,30 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       TRACE2(1, 31);
     }
     __syncwarp();
+  } else if (warp == 10) {
+    // ---------------- second MMA issuer: P(t) = phi(Q) phi(K)^T over the buffer that held S(t) ----------------
+    // (its own warp, on another scheduler than warp 9: the issue streams run in parallel)
+    const bool leader = elect_one();
+    constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
+    const uint64_t dPK0 = smem_desc_sw128(smem_u32(smem + OFF_PK), 16, 1024);
+    mbar_wait(bar_phiq, 0, a.status, 39);
+    for (int t = 0; t < nt; ++t) {
+      const int s = t & 1;
+      mbar_wait(a_done + s, (t >> 1) & 1, a.status, 26);
+      mbar_wait(pk_full + s, (t >> 1) & 1, a.status, 27);
+      tc_fence_after_sync();
+      if (leader) {
+        TRACE2(1, 2 + 8 * t);
+        const uint64_t dPK = dPK0 + (uint64_t)(s * (65536 >> 4));
+        const uint32_t td = tb + T_BUF + s * 128;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
+        mma_commit(pk_empty + s);
+        mma_commit(p_full + s);
+      }
+      __syncwarp();
+    }
   } else {
     // ---------------- softmax warps ----------------
     const int qd = warp & 3, hf = warp >> 2;         // lane quarter (rows), column half
@@ -736,6 +791,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         int clo, chi;
         col_range(u, clo, chi);
         const int wlo = __reduce_min_sync(0xffffffffu, clo), whi = __reduce_max_sync(0xffffffffu, chi);
+        const int wlo_max = __reduce_max_sync(0xffffffffu, clo), whi_min = __reduce_min_sync(0xffffffffu, chi);
         mbar_wait(s_full + s, (u >> 1) & 1, a.status, 35);
         tc_fence_after_sync();
         if (u < 3) TRACE(5 + 4 * u);
@@ -750,17 +806,28 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           uint32_t rs[32];
           tmem_ld32(lane_base + T_BUF + s * 128 + c0, rs);
           tmem_ld_wait();
-          const unsigned span = (unsigned)(chi - clo);
           float l0 = 0.f, l1 = 0.f;
+          if (c0 >= wlo_max && c0 + 31 <= whi_min) {   // every row of this warp sees all 32 keys: no masks
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
-            const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
-            const float e0 = ok0 ? ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co)) : 0.f;
-            const float e1 = ok1 ? ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co)) : 0.f;
-            l0 += e0;
-            l1 += e1;
-            En[16 * c + j] = pack_bf16(e0, e1);
+            for (int j = 0; j < 16; ++j) {
+              const float e0 = ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co));
+              const float e1 = ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co));
+              l0 += e0;
+              l1 += e1;
+              En[16 * c + j] = pack_bf16(e0, e1);
+            }
+          } else {
+            const unsigned span = (unsigned)(chi - clo);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
+              const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
+              const float e0 = ok0 ? ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co)) : 0.f;
+              const float e1 = ok1 ? ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co)) : 0.f;
+              l0 += e0;
+              l1 += e1;
+              En[16 * c + j] = pack_bf16(e0, e1);
+            }
           }
           L += l0 + l1;
         }
@@ -774,6 +841,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         int clo, chi;
         col_range(t, clo, chi);
         const int wlo = __reduce_min_sync(0xffffffffu, clo), whi = __reduce_max_sync(0xffffffffu, chi);
+        const int wlo_max = __reduce_max_sync(0xffffffffu, clo), whi_min = __reduce_min_sync(0xffffffffu, chi);
         mbar_wait(p_full + s, (t >> 1) & 1, a.status, 36);
         if (t >= 1) mbar_wait(d_free, (t - 1) & 1, a.status, 37);
         tc_fence_after_sync();
@@ -789,17 +857,27 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
             uint32_t rp[32];
             tmem_ld32(lane_base + T_BUF + s * 128 + c0, rp);
             tmem_ld_wait();
-            const unsigned span = (unsigned)(chi - clo);
             float d0 = 0.f, d1 = 0.f;
+            if (c0 >= wlo_max && c0 + 31 <= whi_min) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
-              const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
-              const float pv0 = ok0 ? __uint_as_float(rp[2 * j]) : 0.f;
-              const float pv1 = ok1 ? __uint_as_float(rp[2 * j + 1]) : 0.f;
-              d0 += pv0;
-              d1 += pv1;
-              dpk[j] = pack_bf16(bf16_lo(Ec[16 * c + j]) - pv0, bf16_hi(Ec[16 * c + j]) - pv1);
+              for (int j = 0; j < 16; ++j) {
+                const float pv0 = __uint_as_float(rp[2 * j]), pv1 = __uint_as_float(rp[2 * j + 1]);
+                d0 += pv0;
+                d1 += pv1;
+                dpk[j] = pack_bf16(bf16_lo(Ec[16 * c + j]) - pv0, bf16_hi(Ec[16 * c + j]) - pv1);
+              }
+            } else {
+              const unsigned span = (unsigned)(chi - clo);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
+                const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
+                const float pv0 = ok0 ? __uint_as_float(rp[2 * j]) : 0.f;
+                const float pv1 = ok1 ? __uint_as_float(rp[2 * j + 1]) : 0.f;
+                d0 += pv0;
+                d1 += pv1;
+                dpk[j] = pack_bf16(bf16_lo(Ec[16 * c + j]) - pv0, bf16_hi(Ec[16 * c + j]) - pv1);
+              }
             }
             dps += d0 + d1;
           }
@@ -973,7 +1051,10 @@ cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, 
                            float* ksum, cudaStream_t st) {
   cudaError_t e = launch_keys<false>(p, ws, base, beta, nullptr, st);
   if (e != cudaSuccess) return e;
-  return f32_combine_partials(p, ws, base, kv, ksum, st);
+  const int bh = p.B * p.H;
+  const int64_t n = (int64_t)bh * kM * (kPartialLd / 4);
+  tc_combine_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(tc_layout(p, ws, base).partial, ws.nsplit, bh, kv, ksum);
+  return cudaGetLastError();
 }
 
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta, const float* kv,
