@@ -154,8 +154,9 @@ constexpr int NFEAT = 256;                 // feature threads: warps 0-7; warp w
 constexpr int NTHREADS = NFEAT + 64;       // + producer warp 8 + MMA warp 9
 constexpr uint32_t OFF_W = 0;                    // 16 KB  [128 r][64 e]
 constexpr uint32_t OFF_K = 16384;                // ring of [128 keys][64 e] tiles, 16 KB each: 2 deep (4 deep in the beta pass)
-constexpr uint32_t OFF_V = 49152;                // { V 16 KB, ones 16 KB }: [V | 1] is one MN-major operand, N = 80
-constexpr uint32_t OFF_A = OFF_V + 32768;        // 2 x 64 KB: 4 blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
+constexpr uint32_t OFF_V = 49152;                // 2 x 16 KB V tiles; [V | 1] is one MN-major operand (N = 80) whose second
+constexpr uint32_t OFF_ONES = OFF_V + 32768;     // 64-column block is this 16 KB block of ones (leading offset per V slot)
+constexpr uint32_t OFF_A = OFF_ONES + 16384;     // 2 x 64 KB: 4 blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
 constexpr uint32_t OFF_BAR = OFF_A + 2 * 65536;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;    // + alignment slack
 // tensor memory columns
@@ -181,8 +182,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint64_t* bar_w = bars + 0;
   uint64_t* bar_done = bars + 1;
-  uint64_t* v_full = bars + 2;    // V tile landed (single buffer, one completion per tile)
-  uint64_t* v_empty = bars + 3;   // V tile consumed by the summary MMAs
+  uint64_t* v_full = bars + 2;    // [2] V tile landed
+  uint64_t* v_empty = bars + 22;  // [2] V tile consumed by the summary MMAs
   uint64_t* k_full = bars + 4;    // [KD] K tile landed
   uint64_t* k_free = bars + 8;    // [KD] K tile consumed: U computed and every row norm read
   uint64_t* uk_full = bars + 12;  // [2] U = K Wt^T computed
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   uint64_t* a_full = bars + 16;   // [2] phi(K) tile written to shared memory
   uint64_t* a_free = bars + 18;   // [2] phi(K) tile consumed (MMAs done + bulk store has read it)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
-  float* red = reinterpret_cast<float*>(bars + 21);  // [8]
+  float* red = reinterpret_cast<float*>(bars + 24);  // [8]
   constexpr int KD = MAX_ONLY ? 4 : 2;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -206,8 +207,10 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   if (tid == 0) {
     mbar_init(bar_w, 1);
     mbar_init(bar_done, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(v_full + i, 1);
+      mbar_init(v_empty + i, 1);
+    }
     for (int i = 0; i < 4; ++i) {
       mbar_init(k_full + i, 1);
       mbar_init(k_free + i, NFEAT);
@@ -226,7 +229,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   }
   if (!MAX_ONLY)
     for (int i = tid; i < 8192; i += NTHREADS)   // the "ones" block behind the V tile (16 KB of bf16 1.0)
-      reinterpret_cast<__nv_bfloat16*>(smem + OFF_V + 16384)[i] = __float2bfloat16(1.0f);
+      reinterpret_cast<__nv_bfloat16*>(smem + OFF_ONES)[i] = __float2bfloat16(1.0f);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -259,20 +262,13 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         mbar_expect_tx(k_full + ks, 16384);
         tma_load_4d(smem + OFF_K + ks * 16384, &a.tm_k, k_full + ks, 0, row0, h, b);
       }
-      if (!MAX_ONLY && i >= 1) {
-        // V(i-1): single buffer, free once the summary MMAs of tile i-2 are done; it is needed well after K(i)
-        if (i >= 2) mbar_wait(v_empty, (i - 2) & 1, a.status, 11);
+      if (!MAX_ONLY) {
+        const int s = i & 1;
+        if (i >= 2) mbar_wait(v_empty + s, ((i >> 1) - 1) & 1, a.status, 11);
         if (leader) {
-          mbar_expect_tx(v_full, 16384);
-          tma_load_4d(smem + OFF_V, &a.tm_v, v_full, 0, row0 - TILE, h, b);
+          mbar_expect_tx(v_full + s, 16384);
+          tma_load_4d(smem + OFF_V + s * 16384, &a.tm_v, v_full + s, 0, row0, h, b);
         }
-      }
-    }
-    if (!MAX_ONLY && nt >= 1) {
-      if (nt >= 2) mbar_wait(v_empty, (nt - 2) & 1, a.status, 11);
-      if (leader) {
-        mbar_expect_tx(v_full, 16384);
-        tma_load_4d(smem + OFF_V, &a.tm_v, v_full, 0, (t_lo + nt - 1) * TILE, h, b);
       }
     }
     __syncwarp();
@@ -284,11 +280,13 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     const uint64_t dW = smem_desc_sw128(smem_u32(smem + OFF_W), 16, 1024);
     const uint64_t dA0 = smem_desc_sw128(smem_u32(smem + OFF_A), 16384, 1024);
     const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_K), 16, 1024);
-    const uint64_t dV = smem_desc_sw128(smem_u32(smem + OFF_V), 16384, 1024);  // second MN block = ones
+    // second MN block of [V | 1] = the ones block: 32 KB behind V slot 0, 16 KB behind V slot 1
+    const uint64_t dV0 = smem_desc_sw128(smem_u32(smem + OFF_V), 32768, 1024);
+    const uint64_t dV1 = smem_desc_sw128(smem_u32(smem + OFF_V + 16384), 16384, 1024);
     auto issue_kv = [&](int u) {
       const int s = u & 1;
       mbar_wait(a_full + s, (u >> 1) & 1, a.status, 12);
-      mbar_wait(v_full, u & 1, a.status, 14);
+      mbar_wait(v_full + s, (u >> 1) & 1, a.status, 14);
       tc_fence_after_sync();
       if (leader) {
         if (!MAX_ONLY) TRACE2(1, 2 * u);
@@ -301,6 +299,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         }
         tma_store_commit();
         const uint64_t dA = dA0 + (uint64_t)(s * (65536 >> 4));
+        const uint64_t dV = s ? dV1 : dV0;
 #pragma unroll
         for (int mb = 0; mb < 2; ++mb)
 #pragma unroll
@@ -308,7 +307,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
             mma_ss(tb + T_KV + mb * 128, dA + (uint64_t)(mb * (32768 >> 4) + k * (2048 >> 4)),
                    dV + (uint64_t)(k * (2048 >> 4)), id_kv, (u > 0) || (k > 0));
         mma_commit(a_free + s);
-        mma_commit(v_empty);
+        mma_commit(v_empty + s);
         // the previous tile's bulk copy has read its buffer once at most one group is pending
         if (u >= 1) {
           tma_store_wait_read1();
@@ -480,15 +479,18 @@ struct BandArgs {
 
 namespace band {
 constexpr int BQ = 128, KT = 128;
-constexpr int NSOFT = 256;                 // softmax threads: warps 0-7; warp w owns rows 32*(w%4).., column half w/4
-constexpr int NTHREADS = NSOFT + 96;       // + producer warp 8 + MMA warps 9 (S, O, low-rank) and 10 (P)
+constexpr int NCQ = 4;                     // column groups per row: a softmax thread owns 128/NCQ key columns of a tile
+constexpr int NSOFT = 128 * NCQ;           // softmax threads: warp w owns rows 32*(w%4).., column group w/4
+constexpr int CH = 4 / NCQ;                // 32-column chunks per thread and tile
+constexpr int WP = NSOFT / 32;             // first non-softmax warp: producer; WP+1: MMA (S, O, low-rank); WP+2: MMA (P)
+constexpr int NTHREADS = NSOFT + 96;
 constexpr uint32_t OFF_Q = 0;              // 16 KB [128 q][64 e]
 constexpr uint32_t OFF_KV = 16384;         // 32 KB [256 f][64 d]; its first 16 KB hold Wt [128 r][64 e] until U is computed
 constexpr uint32_t OFF_K = 49152;          // 16 KB [128 keys][64 e]
 constexpr uint32_t OFF_V = OFF_K + 16384;  // 16 KB [128 keys][64 d]
 constexpr uint32_t OFF_PK = OFF_V + 16384; // 2 x 64 KB: phi(K) tiles, each 4 blocks [128 keys][64 f]
 constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + exchange fp32[3][256]
-constexpr uint32_t OFF_BAR = OFF_MISC + 4096;
+constexpr uint32_t OFF_BAR = OFF_MISC + 1024 + 12 * NSOFT;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;
 // tensor memory columns
 constexpr uint32_t T_PHIQ = 0;     // 128: phi(Q) packed bf16 (256 features)
@@ -521,7 +523,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   uint64_t* pk_empty = bars + 28;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
   float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);
-  float* s_xch = s_ksum + kM;       // [3][256]
+  float* s_xch = s_ksum + kM;       // [3][NSOFT]
 
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   const int nt = hi >= lo ? (hi - j0) / KT + 1 : 0;
 
   if (tid == 0) TRACE(0);
-  if (warp == 9) {
+  if (warp == WP + 1) {
     // one barrier per lane; arrival counts: the softmax-side barriers take NSOFT arrivals, the rest one
     if (lane < 34) {
       const bool soft = lane == 3 || lane == 16 || lane == 17 || lane == 20 || lane == 21;
@@ -547,7 +549,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     }
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == WP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -560,7 +562,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 40);
   if (tid == 0) TRACE(1);
 
-  if (warp == 8) {
+  if (warp == WP) {
     // ---------------- producer (whole warp waits, one lane issues) ----------------
     const bool leader = elect_one();
     if (leader) {
@@ -621,7 +623,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
+  } else if (warp == WP + 1) {
     // ---------------- MMA issuer (whole warp waits, one lane issues) ----------------
     const bool leader = elect_one();
     constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
@@ -700,7 +702,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       TRACE2(1, 31);
     }
     __syncwarp();
-  } else if (warp == 10) {
+  } else if (warp == WP + 2) {
     // ---------------- second MMA issuer: P(t) = phi(Q) phi(K)^T over the buffer that held S(t) ----------------
     // (its own warp, on another scheduler than warp 9: the issue streams run in parallel)
     const bool leader = elect_one();
@@ -726,13 +728,14 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     }
   } else {
     // ---------------- softmax warps ----------------
-    const int qd = warp & 3, hf = warp >> 2;         // lane quarter (rows), column half
+    const int qd = warp & 3, cq = warp >> 2;         // lane quarter (rows), column group
     const int row = qd * 32 + lane;                  // query row of this thread
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
     const int gi = (int)p.q_pos0 + i0 + row;         // global query position
+    constexpr int PW = 128 / NCQ;                    // projections (and key columns per tile) owned by this thread
     for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)bh * kM + i];
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    // ---- phi(Q): this thread's 64 projections -> 128 features ----
+    asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
+    // ---- phi(Q): this thread's PW projections -> 2*PW features ----
     mbar_wait(bar_qw, 0, a.status, 33);
     const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
     const float g = 0.5f * p.softmax_temp * qn2;
@@ -744,8 +747,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     {
       const float mo = -M * kLog2e;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int f0 = 64 * hf + 32 * c;             // first projection index of this chunk
+      for (int c = 0; c < CH; ++c) {
+        const int f0 = PW * cq + 32 * c;             // first projection index of this chunk
         uint32_t r[32];
         tmem_ld32(lane_base + T_UQ + f0, r);
         tmem_ld_wait();
@@ -774,7 +777,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     const float pls = (-g + M - half_log_m) + a.beta[bh];          // query log-scale + key log-scale
     const float sc = p.softmax_temp * kLog2e, co = -pls * kLog2e;  // exp(tau s - pls) = ex2(s * sc + co)
     float L = 0.f, dps = 0.f;
-    uint32_t Ec[32], En[32];   // exp(tau S - pls), packed bf16: tile being finished / tile just started
+    uint32_t Ec[16 * CH], En[16 * CH];   // exp(tau S - pls), packed bf16: tile being finished / tile just started
 
     // valid tile-local columns of this row in tile t: [clo, chi]
     auto col_range = [&](int t, int& clo, int& chi) {
@@ -796,8 +799,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         tc_fence_after_sync();
         if (u < 3) TRACE(5 + 4 * u);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int c0 = 64 * hf + 32 * c;
+        for (int c = 0; c < CH; ++c) {
+          const int c0 = PW * cq + 32 * c;
           if (c0 + 31 < wlo || c0 > whi) {   // no row of this warp sees these 32 keys
 #pragma unroll
             for (int j = 0; j < 16; ++j) En[16 * c + j] = 0u;
@@ -847,8 +850,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         tc_fence_after_sync();
         if (t < 3) TRACE(7 + 4 * t);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int c0 = 64 * hf + 32 * c;
+        for (int c = 0; c < CH; ++c) {
+          const int c0 = PW * cq + 32 * c;
           uint32_t dpk[16];
           if (c0 + 31 < wlo || c0 > whi) {
 #pragma unroll
@@ -881,7 +884,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
             }
             dps += d0 + d1;
           }
-          tmem_st16(lane_base + T_D + 32 * hf + 16 * c, dpk);
+          tmem_st16(lane_base + T_D + c0 / 2, dpk);
         }
         tmem_st_wait();
         tc_fence_before_sync();
@@ -889,44 +892,50 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         if (t < 3) TRACE(8 + 4 * t);
       }
 #pragma unroll
-      for (int j = 0; j < 32; ++j) Ec[j] = En[j];
+      for (int j = 0; j < 16 * CH; ++j) Ec[j] = En[j];
     }
-    // ---- combine the two column halves of each row ----
+    // ---- combine the column groups of each row ----
     s_xch[tid] = L;
-    s_xch[256 + tid] = dps;
-    s_xch[512 + tid] = (z0 + z1) + (z2 + z3);
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const int mate = tid ^ 128;
-    L += s_xch[mate];
-    dps += s_xch[256 + mate];
-    const float Z = s_xch[512 + tid] + s_xch[512 + mate];
-    // ---- epilogue: this thread writes 32 of the row's 64 outputs ----
+    s_xch[NSOFT + tid] = dps;
+    s_xch[2 * NSOFT + tid] = (z0 + z1) + (z2 + z3);
+    asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
+    float Z = 0.f;
+    L = 0.f;
+    dps = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCQ; ++j) {
+      const int m8 = (tid & 127) + 128 * j;
+      L += s_xch[m8];
+      dps += s_xch[NSOFT + m8];
+      Z += s_xch[2 * NSOFT + m8];
+    }
+    // ---- epilogue: this thread writes 64/NCQ of the row's 64 outputs ----
     mbar_wait(bar_lr, 0, a.status, 38);
     tc_fence_after_sync();
     TRACE(20);
     const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
+    constexpr int OW = 64 / NCQ;
     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
-                          (int64_t)(i0 + row) * p.o_stride_t + 32 * hf;
+                          (int64_t)(i0 + row) * p.o_stride_t + OW * cq;
     {
       // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
-      uint32_t ro[32];
-      tmem_ld32(lane_base + T_O + 32 * hf, ro);
+      uint32_t ro[16];
+      tmem_ld16(lane_base + T_O + OW * cq, ro);
       tmem_ld_wait();
-      uint32_t o[16];
+      uint32_t o[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
+      for (int j = 0; j < 8; ++j)
         o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
       if (row < nq) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          reinterpret_cast<uint4*>(orow)[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        reinterpret_cast<uint4*>(orow)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<uint4*>(orow)[1] = make_uint4(o[4], o[5], o[6], o[7]);
       }
     }
   }
   if (tid == 0) TRACE(21);
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == WP) {
     __syncwarp();
     tmem_dealloc(tb, 512);
   }
