@@ -56,6 +56,8 @@ bool tc_supported(const SblParams& p);
 cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
                                   bool reset_status);
 cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
+// one-pass upper bound on the key log-scale (valid stabiliser when eps = 0); used by the fused forward
+cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
 cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta,
                            float* kv, float* ksum, cudaStream_t st);
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,

@@ -101,6 +101,48 @@ __global__ void __launch_bounds__(1024) tc_prep_kernel(const float* W, float c, 
   if (reset_status && threadIdx.x < 4) status[threadIdx.x] = 0;
 }
 
+// Upper bound on the key log-scale from row norms alone: every feature exponent
+// +-u_f - tau|k|^2/2 - ln(m)/2 is at most wmax|k| - tau|k|^2/2 - ln(m)/2 (Cauchy-Schwarz, wmax = largest row norm
+// of the scaled projection).  With eps = 0 any stabiliser >= the true maximum gives the same output, so the
+// fused forward uses this one-pass, memory-bound bound instead of the exact maximum over all m features.
+// Eight lanes per key row (16 bytes each), 512 rows per block.
+__global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* k, int64_t sb, int64_t ss, int64_t sh,
+                                                           int H, int row_lo, int row_hi, float tau, float half_log_m,
+                                                           const float* wmax, float* beta) {
+  __shared__ float red[8];
+  const int bh = blockIdx.y, b = bh / H, h = bh % H;
+  const __nv_bfloat16* base = k + b * sb + h * sh;
+  const float wm = __ldg(wmax);
+  const int sub = threadIdx.x & 7;
+  float best = -INFINITY;
+  for (int it = 0; it < 16; ++it) {
+    const int row = row_lo + blockIdx.x * 512 + it * 32 + (threadIdx.x >> 3);
+    float s = 0.f;
+    if (row < row_hi) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)row * ss) + sub);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float x = bf16_lo(w[j]), y = bf16_hi(w[j]);
+        s = fmaf(x, x, s);
+        s = fmaf(y, y, s);
+      }
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (row < row_hi) best = fmaxf(best, wm * sqrtf(s) - 0.5f * tau * s - half_log_m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+  if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) best = fmaxf(best, red[i]);
+    if (best > -INFINITY) atomic_max_float(beta + bh, best);
+  }
+}
+
 // kv (BH,256,64), ksum (BH,256) = sum over the splits of the per-CTA partial summaries
 __global__ void tc_combine_kernel(const float* partial, int nsplit, int BH, float* kv, float* ksum) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over BH * 256 * 20 float4 groups
@@ -1054,6 +1096,21 @@ cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base,
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return launch_keys<true>(p, ws, base, nullptr, beta, st);
+}
+
+cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st) {
+  const TcLayout l = tc_layout(p, ws, base);
+  const int bh = p.B * p.H;
+  tc_fill_kernel<<<(unsigned)div_up(bh, 256), 256, 0, st>>>(beta, -INFINITY, bh);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int rows = p.sum_hi - p.sum_lo;
+  if (rows <= 0) return cudaSuccess;
+  dim3 grid((unsigned)div_up(rows, 512), (unsigned)bh);
+  tc_key_bound_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p.k), p.k_stride_b, p.k_stride_s,
+                                           p.k_stride_h, p.H, p.sum_lo, p.sum_hi, p.softmax_temp,
+                                           (float)(log((double)kM) / 2.0), l.wmax, beta);
+  return cudaGetLastError();
 }
 
 cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta, float* kv,
