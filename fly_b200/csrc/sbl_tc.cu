@@ -170,9 +170,11 @@ __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64
 __device__ long long g_trace[64][32];
 __device__ long long g_trace2[64][2][32];   // [cta][0 = producer, 1 = MMA issuer][slot]
 #define TRACE(slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (threadIdx.x == 0)) g_trace[blockIdx.y * 8 + blockIdx.x][slot] = clock64(); } while (0)
+#define TRACEB(slot) do { if (it == 2 && blockIdx.x < 64 && threadIdx.x == 0) g_trace[blockIdx.x][slot] = clock64(); } while (0)
 #define TRACE2(who, slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (slot) < 32) g_trace2[blockIdx.y * 8 + blockIdx.x][who][slot] = clock64(); } while (0)
 #else
 #define TRACE(slot) do { } while (0)
+#define TRACEB(slot) do { } while (0)
 #define TRACE2(who, slot) do { } while (0)
 #endif
 
@@ -516,78 +518,98 @@ struct BandArgs {
   const float* ksum;
   const float* wmax;     // [1]: max_f |sqrt(tau) w_f| of the bf16 projection
   int* status;
+  int ntq;               // query tiles per (b,h)
+  int ntiles;            // ntq * B * H
 };
-
 
 namespace band {
 constexpr int BQ = 128, KT = 128;
 constexpr int NCQ = 4;                     // column groups per row: a softmax thread owns 128/NCQ key columns of a tile
 constexpr int NSOFT = 128 * NCQ;           // softmax threads: warp w owns rows 32*(w%4).., column group w/4
 constexpr int CH = 4 / NCQ;                // 32-column chunks per thread and tile
-constexpr int WP = NSOFT / 32;             // first non-softmax warp: producer; WP+1: MMA (S, O, low-rank); WP+2: MMA (P)
+constexpr int WP = NSOFT / 32;             // first non-softmax warp: producer; WP+1: MMA (U, S, O, low-rank); WP+2: MMA (P)
 constexpr int NTHREADS = NSOFT + 96;
 constexpr uint32_t OFF_Q = 0;              // 16 KB [128 q][64 e]
 constexpr uint32_t OFF_KV = 16384;         // 32 KB [256 f][64 d]; its first 16 KB hold Wt [128 r][64 e] until U is computed
 constexpr uint32_t OFF_K = 49152;          // 16 KB [128 keys][64 e]
 constexpr uint32_t OFF_V = OFF_K + 16384;  // 16 KB [128 keys][64 d]
 constexpr uint32_t OFF_PK = OFF_V + 16384; // 2 x 64 KB: phi(K) tiles, each 4 blocks [128 keys][64 f]
-constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + exchange fp32[3][256]
+constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + exchange fp32[3][NSOFT]
 constexpr uint32_t OFF_BAR = OFF_MISC + 1024 + 12 * NSOFT;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;
 // tensor memory columns
 constexpr uint32_t T_PHIQ = 0;     // 128: phi(Q) packed bf16 (256 features)
-constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, later P of the same tile
+constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, later P of the same tile; U of the next query tile
 constexpr uint32_t T_O = 384;      // 64
 constexpr uint32_t T_D = 448;      // 64: D packed bf16 (128 keys)
-constexpr uint32_t T_UQ = 256;     // aliases buffer 1 before the band loop
+// barrier indices
+enum {
+  B_Q = 0,       // Q tile landed                      (per query tile)
+  B_W,           // Wt landed                          (per query tile)
+  B_KV,          // KV landed                          (per query tile)
+  B_UQ,          // U = Q Wt^T computed                (per query tile)
+  B_PHIQ,        // phi(Q) stored, O read              (per query tile, NSOFT arrivals)
+  B_DONE,        // all MMAs of the query tile done    (per query tile)
+  B_QFREE,       // Q buffer reusable                  (per query tile, 1 + NSOFT arrivals)
+  B_WFREE,       // Wt/KV buffer reusable              (per query tile)
+  B_DFREE,       // D consumed by O += D V             (per key tile)
+  B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY,              // per key tile, single buffers
+  B_PKFULL, B_PKEMPTY = B_PKFULL + 2,                // [2] per key tile, by ring slot
+  B_SFULL = B_PKEMPTY + 2,                           // [2] by buffer
+  B_ADONE = B_SFULL + 2,                             // [2] NSOFT arrivals
+  B_PFULL = B_ADONE + 2,                             // [2]
+  B_BDONE = B_PFULL + 2,                             // [2] NSOFT arrivals
+  B_COUNT = B_BDONE + 2
+};
+static_assert(B_COUNT <= 32, "one barrier per lane of the initialising warp");
 }  // namespace band
 
+// Geometry of one 128-query tile: which key tiles it visits.
+struct BandTile {
+  int bh, b, h, i0, nq, len_b, j0, nt;
+};
+__device__ __forceinline__ BandTile band_tile(const BandArgs& a, int tile_id) {
+  const SblParams& p = a.p;
+  BandTile t;
+  t.bh = tile_id / a.ntq;
+  t.b = t.bh / p.H;
+  t.h = t.bh % p.H;
+  t.i0 = (tile_id % a.ntq) * band::BQ;
+  t.nq = min(band::BQ, p.T - t.i0);
+  t.len_b = (int)(p.key_lengths ? min(p.key_lengths[t.b], p.S_total) : p.S_total);
+  const int hw = p.w / 2;
+  // key buffer rows any query of this tile can see, clipped to the buffer and to the key length
+  int lo = (int)(p.q_pos0 + t.i0 - hw - p.k_pos0);
+  int hi = (int)(p.q_pos0 + t.i0 + t.nq - 1 - hw + p.w - 1 - p.k_pos0);
+  lo = max(lo, 0);
+  hi = min(hi, min(p.S - 1, t.len_b - 1 - (int)p.k_pos0));
+  t.j0 = (lo / band::KT) * band::KT;
+  t.nt = hi >= lo ? (hi - t.j0) / band::KT + 1 : 0;
+  return t;
+}
+
+// Persistent: CTA c processes query tiles c, c + gridDim.x, ...  Key tiles are numbered
+// globally per CTA (g = 0, 1, ... across query tiles); key tile g uses accumulator buffer g & 1 and
+// phi(K) slot g & 1, and the U of a query tile goes to the buffer its second key tile will use,
+// so that the next query tile's Q/Wt loads and U = Q Wt^T overlap the current tile's tail.
 __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_constant__ BandArgs a) {
   using namespace band;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-  uint64_t* bar_qw = bars + 0;
-  uint64_t* bar_kv = bars + 1;
-  uint64_t* bar_uq = bars + 2;
-  uint64_t* bar_phiq = bars + 3;
-  uint64_t* bar_lr = bars + 4;
-  uint64_t* d_free = bars + 5;
-  uint64_t* k_full = bars + 6;
-  uint64_t* k_empty = bars + 8;
-  uint64_t* v_full = bars + 10;
-  uint64_t* v_empty = bars + 12;
-  uint64_t* s_full = bars + 14;     // [2]
-  uint64_t* a_done = bars + 16;     // [2]
-  uint64_t* p_full = bars + 18;     // [2]
-  uint64_t* b_done = bars + 20;     // [2]
-  uint64_t* pk_full = bars + 22;    // [2]
-  uint64_t* pk_empty = bars + 28;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);
   float* s_xch = s_ksum + kM;       // [3][NSOFT]
 
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  const int i0 = blockIdx.x * BQ;
   const int hw = p.w / 2;
-  const int len_b = (int)(p.key_lengths ? min(p.key_lengths[b], p.S_total) : p.S_total);
-  // key buffer rows any query of this tile can see, clipped to the buffer and to the key length
-  const int nq = min(BQ, p.T - i0);
-  int lo = (int)(p.q_pos0 + i0 - hw - p.k_pos0);
-  int hi = (int)(p.q_pos0 + i0 + nq - 1 - hw + p.w - 1 - p.k_pos0);
-  lo = max(lo, 0);
-  hi = min(hi, min(p.S - 1, len_b - 1 - (int)p.k_pos0));
-  const int j0 = (lo / KT) * KT;
-  const int nt = hi >= lo ? (hi - j0) / KT + 1 : 0;
+  const int n_it = (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // query tiles of this CTA
 
-  if (tid == 0) TRACE(0);
   if (warp == WP + 1) {
-    // one barrier per lane; arrival counts: the softmax-side barriers take NSOFT arrivals, the rest one
-    if (lane < 34) {
-      const bool soft = lane == 3 || lane == 16 || lane == 17 || lane == 20 || lane == 21;
-      mbar_init(bars + lane, soft ? NSOFT : 1);
+    if (lane < B_COUNT) {
+      const bool soft = lane == B_PHIQ || lane == B_ADONE || lane == B_ADONE + 1 || lane == B_BDONE || lane == B_BDONE + 1;
+      mbar_init(bars + lane, lane == B_QFREE ? NSOFT + 1 : (soft ? NSOFT : 1));
     }
     fence_mbar_init();
   }
@@ -602,7 +624,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   // column 0; keeping the base a compile-time constant keeps every MMA operand uniform.
   constexpr uint32_t tb = 0;
   if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 40);
-  if (tid == 0) TRACE(1);
 
   if (warp == WP) {
     // ---------------- producer (whole warp waits, one lane issues) ----------------
@@ -614,59 +635,74 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       prefetch_tmap(&a.tm_w);
       prefetch_tmap(&a.tm_phik);
       prefetch_tmap(&a.tm_kv);
-      mbar_expect_tx(bar_qw, 32768);
-      tma_load_4d(smem + OFF_Q, &a.tm_q, bar_qw, 0, i0, h, b);
-      tma_load_2d(smem + OFF_KV, &a.tm_w, bar_qw, 0, 0);
     }
-    // K and V are single-buffered, phi(K) double-buffered.  Issue order follows the order
-    // in which the tensor core frees the buffers: K(t), phi(K)(t), then V(t-1).
-    auto load_v = [&](int t) {
-      if (t >= 1) mbar_wait(v_empty, (t - 1) & 1, a.status, 23);
+    int gk = 0;   // key tiles loaded so far
+    // Q and Wt of query tile `it2`: issued as soon as the previous tile has released the two buffers,
+    // i.e. in the middle of the previous tile, so that U = Q Wt^T of the next tile is ready at its start
+    auto load_qw = [&](int it2) {
+      if (it2 >= n_it) return;
+      const BandTile T2 = band_tile(a, it2 * gridDim.x + blockIdx.x);
+      if (it2 >= 1) mbar_wait(bars + B_QFREE, (it2 - 1) & 1, a.status, 20);
       if (leader) {
-        mbar_expect_tx(v_full, 16384);
-        tma_load_4d(smem + OFF_V, &a.tm_v, v_full, 0, j0 + t * KT, h, b);
-        TRACE2(0, 6 + 8 * t);
+        mbar_expect_tx(bars + B_Q, 16384);
+        tma_load_4d(smem + OFF_Q, &a.tm_q, bars + B_Q, 0, T2.i0, T2.h, T2.b);
+      }
+      if (it2 >= 1) mbar_wait(bars + B_WFREE, (it2 - 1) & 1, a.status, 21);
+      if (leader) {
+        mbar_expect_tx(bars + B_W, 16384);
+        tma_load_2d(smem + OFF_KV, &a.tm_w, bars + B_W, 0, 0);
       }
     };
-    for (int t = 0; t < nt; ++t) {
-      const int s = t & 1, row0 = j0 + t * KT;
-      if (t >= 1) mbar_wait(k_empty, (t - 1) & 1, a.status, 21);
-      if (leader) {
-        mbar_expect_tx(k_full, 16384);
-        tma_load_4d(smem + OFF_K, &a.tm_k, k_full, 0, row0, h, b);
-        TRACE2(0, 1 + 8 * t);
-      }
-      if (t >= 2) mbar_wait(pk_empty + s, ((t >> 1) - 1) & 1, a.status, 22);
-      if (leader) {
-        mbar_expect_tx(pk_full + s, 65536);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          tma_load_3d(smem + OFF_PK + s * 65536 + j * 16384, &a.tm_phik, pk_full + s, j * 64, row0, bh);
-        TRACE2(0, 2 + 8 * t);
-      }
-      if (t == 0) {
-        load_v(0);
-        // KV shares its buffer with Wt: load it once U = Q Wt^T has been computed
-        mbar_wait(bar_uq, 0, a.status, 24);
+    load_qw(0);
+    for (int it = 0; it < n_it; ++it) {
+      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      // K and V are single-buffered, phi(K) double-buffered.  Issue order follows the order
+      // in which the tensor core frees the buffers: K(g), phi(K)(g), then V(g-1).
+      auto load_v = [&](int t) {
+        const int g = gk + t;
+        if (g >= 1) mbar_wait(bars + B_VEMPTY, (g - 1) & 1, a.status, 23);
         if (leader) {
-          mbar_expect_tx(bar_kv, 32768);
-          tma_load_3d(smem + OFF_KV, &a.tm_kv, bar_kv, 0, 0, bh);
+          mbar_expect_tx(bars + B_VFULL, 16384);
+          tma_load_4d(smem + OFF_V, &a.tm_v, bars + B_VFULL, 0, T.j0 + t * KT, T.h, T.b);
         }
-      } else if (t >= 2) {
-        load_v(t - 1);
+      };
+      auto load_kv = [&]() {
+        // KV shares its buffer with Wt: load it once U = Q Wt^T has been computed
+        mbar_wait(bars + B_UQ, it & 1, a.status, 24);
+        if (leader) {
+          mbar_expect_tx(bars + B_KV, 32768);
+          tma_load_3d(smem + OFF_KV, &a.tm_kv, bars + B_KV, 0, 0, T.bh);
+        }
+      };
+      for (int t = 0; t < T.nt; ++t) {
+        const int g = gk + t, s = g & 1, row0 = T.j0 + t * KT;
+        if (g >= 1) mbar_wait(bars + B_KEMPTY, (g - 1) & 1, a.status, 21);
+        if (leader) {
+          mbar_expect_tx(bars + B_KFULL, 16384);
+          tma_load_4d(smem + OFF_K, &a.tm_k, bars + B_KFULL, 0, row0, T.h, T.b);
+        }
+        if (g >= 2) mbar_wait(bars + B_PKEMPTY + s, ((g >> 1) - 1) & 1, a.status, 22);
+        if (leader) {
+          mbar_expect_tx(bars + B_PKFULL + s, 65536);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tma_load_3d(smem + OFF_PK + s * 65536 + j * 16384, &a.tm_phik, bars + B_PKFULL + s, j * 64, row0, T.bh);
+        }
+        if (t == 0) {
+          load_v(0);
+          load_kv();
+        } else if (t >= 2) {
+          load_v(t - 1);
+        }
       }
-    }
-    if (nt >= 2) load_v(nt - 1);
-    if (nt == 0) {
-      mbar_wait(bar_uq, 0, a.status, 24);
-      if (leader) {
-        mbar_expect_tx(bar_kv, 32768);
-        tma_load_3d(smem + OFF_KV, &a.tm_kv, bar_kv, 0, 0, bh);
-      }
+      if (T.nt == 0) load_kv();
+      load_qw(it + 1);
+      if (T.nt >= 2) load_v(T.nt - 1);
+      gk += T.nt;
     }
     __syncwarp();
   } else if (warp == WP + 1) {
-    // ---------------- MMA issuer (whole warp waits, one lane issues) ----------------
+    // ---------------- MMA issuer A: U, S, low-rank, O (whole warp waits, one lane issues) ----------------
     const bool leader = elect_one();
     constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
     constexpr uint32_t id_o = idesc_bf16(128, 64, false, true);
@@ -674,307 +710,350 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     const uint64_t dKV = smem_desc_sw128(smem_u32(smem + OFF_KV), 16, 1024);
     const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_K), 16, 1024);
     const uint64_t dV0 = smem_desc_sw128(smem_u32(smem + OFF_V), 16, 1024);
-    const uint64_t dPK0 = smem_desc_sw128(smem_u32(smem + OFF_PK), 16, 1024);
-    auto issue_s = [&](int t) {
-      const int s = t & 1;
-      mbar_wait(k_full, t & 1, a.status, 25);
+    int gk = 0;
+    auto b_done_wait = [&](int g) {   // B of key tile g finished: its buffer and D are consumed
+      mbar_wait(bars + B_BDONE + (g & 1), (g >> 1) & 1, a.status, 28);
+    };
+    auto issue_s = [&](int g, bool last) {
+      mbar_wait(bars + B_KFULL, g & 1, a.status, 25);
       tc_fence_after_sync();
       if (leader) {
-        TRACE2(1, 1 + 8 * t);
-        const uint32_t td = tb + T_BUF + s * 128;
+        const uint32_t td = tb + T_BUF + (g & 1) * 128;
         mma_ss(td, dQ, dK0, id_n128, false);
         mma_ss(td, dQ + 2, dK0 + 2, id_n128, true);
         mma_ss(td, dQ + 4, dK0 + 4, id_n128, true);
         mma_ss(td, dQ + 6, dK0 + 6, id_n128, true);
-        mma_commit(k_empty);
-        mma_commit(s_full + s);
+        mma_commit(bars + B_KEMPTY);
+        mma_commit(bars + B_SFULL + (g & 1));
+        if (last) mma_commit(bars + B_QFREE);   // no later MMA of this query tile reads Q
       }
       __syncwarp();
     };
-    auto issue_o = [&](int u) {
-      const int s = u & 1;
-      mbar_wait(b_done + s, (u >> 1) & 1, a.status, 28);
-      mbar_wait(v_full, u & 1, a.status, 29);
+    auto issue_o = [&](int g) {
+      b_done_wait(g);
+      mbar_wait(bars + B_VFULL, g & 1, a.status, 29);
       tc_fence_after_sync();
       if (leader) {
-        TRACE2(1, 7 + 8 * u);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           mma_ts(tb + T_O, tb + T_D + k * 8, dV0 + (uint64_t)(k * (2048 >> 4)), id_o, true);
-        mma_commit(v_empty);
-        mma_commit(d_free);
+        mma_commit(bars + B_VEMPTY);
+        mma_commit(bars + B_DFREE);
       }
       __syncwarp();
     };
-    mbar_wait(bar_qw, 0, a.status, 30);
-    tc_fence_after_sync();
-    if (leader) {
-      TRACE2(1, 0);
-      mma_ss(tb + T_UQ, dQ, dKV, id_n128, false);
-      mma_ss(tb + T_UQ, dQ + 2, dKV + 2, id_n128, true);
-      mma_ss(tb + T_UQ, dQ + 4, dKV + 4, id_n128, true);
-      mma_ss(tb + T_UQ, dQ + 6, dKV + 6, id_n128, true);
-      mma_commit(bar_uq);
-    }
-    __syncwarp();
-    if (nt > 0) issue_s(0);          // S(0) does not need phi(Q): it runs while the softmax warps form it
-    mbar_wait(bar_phiq, 0, a.status, 31);
-    tc_fence_after_sync();
-    if (nt > 1) issue_s(1);
-    // O starts as the low-rank numerator phi(Q) KV; the band tiles accumulate onto it
-    mbar_wait(bar_kv, 0, a.status, 32);
-    tc_fence_after_sync();
-    if (leader) {
-#pragma unroll
-      for (int k = 0; k < 16; ++k)
-        mma_ts(tb + T_O, tb + T_PHIQ + k * 8, dKV + (uint64_t)(k * (2048 >> 4)), id_o, k > 0);
-    }
-    __syncwarp();
-    for (int t = 1; t < nt; ++t) {
-      // both need B(t-1) finished; S first, the softmax warps are waiting for it
-      if (t + 1 < nt) {
-        mbar_wait(b_done + ((t - 1) & 1), ((t - 1) >> 1) & 1, a.status, 28);
-        issue_s(t + 1);
+    for (int it = 0; it < n_it; ++it) {
+      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      const int nt = T.nt;
+      // U = Q Wt^T into the buffer of key tile gk+1; that buffer last held key tile gk-1
+      mbar_wait(bars + B_Q, it & 1, a.status, 30);
+      mbar_wait(bars + B_W, it & 1, a.status, 30);
+      if (gk >= 1) b_done_wait(gk - 1);
+      tc_fence_after_sync();
+      if (leader) {
+        const uint32_t td = tb + T_BUF + ((gk + 1) & 1) * 128;
+        mma_ss(td, dQ, dKV, id_n128, false);
+        mma_ss(td, dQ + 2, dKV + 2, id_n128, true);
+        mma_ss(td, dQ + 4, dKV + 4, id_n128, true);
+        mma_ss(td, dQ + 6, dKV + 6, id_n128, true);
+        mma_commit(bars + B_UQ);
+        if (nt == 0) mma_commit(bars + B_QFREE);
       }
-      issue_o(t - 1);
+      __syncwarp();
+      // S(0) does not need phi(Q): it runs while the softmax warps form it (its buffer last held key tile gk-2)
+      if (nt > 0) {
+        if (gk >= 2) b_done_wait(gk - 2);
+        issue_s(gk, nt == 1);
+      }
+      mbar_wait(bars + B_PHIQ, it & 1, a.status, 31);
+      tc_fence_after_sync();
+      if (nt > 1) issue_s(gk + 1, nt == 2);
+      // O starts as the low-rank numerator phi(Q) KV; the band tiles accumulate onto it
+      mbar_wait(bars + B_KV, it & 1, a.status, 32);
+      tc_fence_after_sync();
+      if (leader) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          mma_ts(tb + T_O, tb + T_PHIQ + k * 8, dKV + (uint64_t)(k * (2048 >> 4)), id_o, k > 0);
+        mma_commit(bars + B_WFREE);
+      }
+      __syncwarp();
+      for (int t = 1; t < nt; ++t) {
+        // both need B(t-1) finished; S first, the softmax warps are waiting for it
+        if (t + 1 < nt) {
+          b_done_wait(gk + t - 1);
+          issue_s(gk + t + 1, t + 2 == nt);
+        }
+        issue_o(gk + t - 1);
+      }
+      if (nt > 0) issue_o(gk + nt - 1);
+      if (leader) mma_commit(bars + B_DONE);
+      __syncwarp();
+      gk += nt;
     }
-    if (nt > 0) issue_o(nt - 1);
-    if (leader) {
-      mma_commit(bar_lr);
-      TRACE2(1, 31);
-    }
-    __syncwarp();
   } else if (warp == WP + 2) {
-    // ---------------- second MMA issuer: P(t) = phi(Q) phi(K)^T over the buffer that held S(t) ----------------
-    // (its own warp, on another scheduler than warp 9: the issue streams run in parallel)
+    // ---------------- MMA issuer B: P(g) = phi(Q) phi(K)^T over the buffer that held S(g) ----------------
+    // (its own warp, on another scheduler than issuer A: the two issue streams run in parallel)
     const bool leader = elect_one();
     constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
     const uint64_t dPK0 = smem_desc_sw128(smem_u32(smem + OFF_PK), 16, 1024);
-    mbar_wait(bar_phiq, 0, a.status, 39);
-    for (int t = 0; t < nt; ++t) {
-      const int s = t & 1;
-      mbar_wait(a_done + s, (t >> 1) & 1, a.status, 26);
-      mbar_wait(pk_full + s, (t >> 1) & 1, a.status, 27);
-      tc_fence_after_sync();
-      if (leader) {
-        TRACE2(1, 2 + 8 * t);
-        const uint64_t dPK = dPK0 + (uint64_t)(s * (65536 >> 4));
-        const uint32_t td = tb + T_BUF + s * 128;
+    int gk = 0;
+    for (int it = 0; it < n_it; ++it) {
+      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      mbar_wait(bars + B_PHIQ, it & 1, a.status, 39);
+      for (int t = 0; t < T.nt; ++t) {
+        const int g = gk + t, s = g & 1;
+        mbar_wait(bars + B_ADONE + s, (g >> 1) & 1, a.status, 26);
+        mbar_wait(bars + B_PKFULL + s, (g >> 1) & 1, a.status, 27);
+        tc_fence_after_sync();
+        if (leader) {
+          const uint64_t dPK = dPK0 + (uint64_t)(s * (65536 >> 4));
+          const uint32_t td = tb + T_BUF + s * 128;
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
-        mma_commit(pk_empty + s);
-        mma_commit(p_full + s);
+          for (int k = 0; k < 16; ++k)
+            mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
+          mma_commit(bars + B_PKEMPTY + s);
+          mma_commit(bars + B_PFULL + s);
+        }
+        __syncwarp();
       }
-      __syncwarp();
+      gk += T.nt;
     }
   } else {
     // ---------------- softmax warps ----------------
     const int qd = warp & 3, cq = warp >> 2;         // lane quarter (rows), column group
     const int row = qd * 32 + lane;                  // query row of this thread
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
-    const int gi = (int)p.q_pos0 + i0 + row;         // global query position
     constexpr int PW = 128 / NCQ;                    // projections (and key columns per tile) owned by this thread
-    for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)bh * kM + i];
-    asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
-    // ---- phi(Q): this thread's PW projections -> 2*PW features ----
-    mbar_wait(bar_qw, 0, a.status, 33);
-    const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
-    const float g = 0.5f * p.softmax_temp * qn2;
-    const float M = sqrtf(qn2) * __ldg(a.wmax);      // >= |u_f| for every feature (Cauchy-Schwarz)
-    mbar_wait(bar_uq, 0, a.status, 34);
-    tc_fence_after_sync();
-    TRACE(3);
-    float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
-    {
-      const float mo = -M * kLog2e;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const int f0 = PW * cq + 32 * c;             // first projection index of this chunk
-        uint32_t r[32];
-        tmem_ld32(lane_base + T_UQ + f0, r);
-        tmem_ld_wait();
-        uint32_t p1[16], p2[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float u0 = __uint_as_float(r[2 * j]) * kLog2e, u1 = __uint_as_float(r[2 * j + 1]) * kLog2e;
-          p1[j] = pack_bf16(ex2(u0 + mo), ex2(u1 + mo));
-          p2[j] = pack_bf16(ex2(mo - u0), ex2(mo - u1));
-          // Z from the rounded features, so that Z - dps cancels what the MMA sees
-          z0 = fmaf(bf16_lo(p1[j]), s_ksum[f0 + 2 * j], z0);
-          z1 = fmaf(bf16_hi(p1[j]), s_ksum[f0 + 2 * j + 1], z1);
-          z2 = fmaf(bf16_lo(p2[j]), s_ksum[kR + f0 + 2 * j], z2);
-          z3 = fmaf(bf16_hi(p2[j]), s_ksum[kR + f0 + 2 * j + 1], z3);
-        }
-        tmem_st16(lane_base + T_PHIQ + f0 / 2, p1);
-        tmem_st16(lane_base + T_PHIQ + 64 + f0 / 2, p2);
-      }
-      tmem_st_wait();
-    }
-    tc_fence_before_sync();
-    mbar_arrive(bar_phiq);
-    TRACE(4);
-
+    constexpr int OW = 64 / NCQ;                     // output columns owned by this thread
+    const float wmax = __ldg(a.wmax);
     const float half_log_m = 0.5f * logf((float)kM);
-    const float pls = (-g + M - half_log_m) + a.beta[bh];          // query log-scale + key log-scale
-    const float sc = p.softmax_temp * kLog2e, co = -pls * kLog2e;  // exp(tau s - pls) = ex2(s * sc + co)
-    float L = 0.f, dps = 0.f;
-    uint32_t Ec[16 * CH], En[16 * CH];   // exp(tau S - pls), packed bf16: tile being finished / tile just started
-
-    // valid tile-local columns of this row in tile t: [clo, chi]
-    auto col_range = [&](int t, int& clo, int& chi) {
-      const int gk0 = (int)p.k_pos0 + j0 + t * KT;
-      clo = max(gi - hw - gk0, 0);
-      chi = min(min(gi - hw + p.w - 1 - gk0, len_b - 1 - gk0), KT - 1);
-    };
-    // Software pipeline over key tiles: A(t+1) (exponentials of S) runs while the
-    // tensor core computes P(t); B(t) then forms D(t).
-    for (int t = -1; t < nt; ++t) {
-      if (t + 1 < nt) {
-        // A: S(t+1) -> masked exponentials (kept packed), row sum L
-        const int u = t + 1, s = u & 1;
-        int clo, chi;
-        col_range(u, clo, chi);
-        const int wlo = __reduce_min_sync(0xffffffffu, clo), whi = __reduce_max_sync(0xffffffffu, chi);
-        const int wlo_max = __reduce_max_sync(0xffffffffu, clo), whi_min = __reduce_min_sync(0xffffffffu, chi);
-        mbar_wait(s_full + s, (u >> 1) & 1, a.status, 35);
-        tc_fence_after_sync();
-        if (u < 3) TRACE(5 + 4 * u);
+    const float sc = p.softmax_temp * kLog2e;
+    int gk = 0;
+    for (int it = 0; it < n_it; ++it) {
+      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      const int nt = T.nt;
+      const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
+      const int gi_first = (int)p.q_pos0 + T.i0 + qd * 32, gi_last = gi_first + 31;   // rows of this warp
+      TRACEB(0);
+      // s_ksum / s_xch are free again: every thread passed the exchange of the previous tile
+      for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)T.bh * kM + i];
+      asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
+      // ---- phi(Q): this thread's PW projections -> 2*PW features ----
+      TRACEB(1);
+      mbar_wait(bars + B_Q, it & 1, a.status, 33);
+      TRACEB(2);
+      const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
+      mbar_arrive(bars + B_QFREE);
+      const float g = 0.5f * p.softmax_temp * qn2;
+      const float M = sqrtf(qn2) * wmax;             // >= |u_f| for every feature (Cauchy-Schwarz)
+      mbar_wait(bars + B_UQ, it & 1, a.status, 34);
+      tc_fence_after_sync();
+      TRACEB(3);
+      float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
+      {
+        const float mo = -M * kLog2e;
+        const uint32_t t_uq = lane_base + T_BUF + ((gk + 1) & 1) * 128;
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const int c0 = PW * cq + 32 * c;
-          if (c0 + 31 < wlo || c0 > whi) {   // no row of this warp sees these 32 keys
-#pragma unroll
-            for (int j = 0; j < 16; ++j) En[16 * c + j] = 0u;
-            continue;
-          }
-          uint32_t rs[32];
-          tmem_ld32(lane_base + T_BUF + s * 128 + c0, rs);
+        for (int c = 0; c < 2 * CH; ++c) {
+          const int f0 = PW * cq + 16 * c;           // first projection index of this group of 16
+          uint32_t r[16];
+          tmem_ld16(t_uq + f0, r);
           tmem_ld_wait();
-          float l0 = 0.f, l1 = 0.f;
-          if (c0 >= wlo_max && c0 + 31 <= whi_min) {   // every row of this warp sees all 32 keys: no masks
+          uint32_t p1[8], p2[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float e0 = ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co));
-              const float e1 = ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co));
-              l0 += e0;
-              l1 += e1;
-              En[16 * c + j] = pack_bf16(e0, e1);
+          for (int j = 0; j < 8; ++j) {
+            const float u0 = __uint_as_float(r[2 * j]) * kLog2e, u1 = __uint_as_float(r[2 * j + 1]) * kLog2e;
+            p1[j] = pack_bf16(ex2(u0 + mo), ex2(u1 + mo));
+            p2[j] = pack_bf16(ex2(mo - u0), ex2(mo - u1));
+            // Z from the rounded features, so that Z - dps cancels what the MMA sees
+            z0 = fmaf(bf16_lo(p1[j]), s_ksum[f0 + 2 * j], z0);
+            z1 = fmaf(bf16_hi(p1[j]), s_ksum[f0 + 2 * j + 1], z1);
+            z2 = fmaf(bf16_lo(p2[j]), s_ksum[kR + f0 + 2 * j], z2);
+            z3 = fmaf(bf16_hi(p2[j]), s_ksum[kR + f0 + 2 * j + 1], z3);
+          }
+          tmem_st8(lane_base + T_PHIQ + f0 / 2, p1);
+          tmem_st8(lane_base + T_PHIQ + 64 + f0 / 2, p2);
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bars + B_PHIQ);
+      TRACEB(4);
+
+      const float pls = (-g + M - half_log_m) + a.beta[T.bh];       // query log-scale + key log-scale
+      const float co = -pls * kLog2e;                               // exp(tau s - pls) = ex2(s * sc + co)
+      float L = 0.f, dps = 0.f;
+      uint32_t Ec[16 * CH], En[16 * CH];   // exp(tau S - pls), packed bf16: tile being finished / tile just started
+
+      // valid tile-local columns [clo, chi] of query position q in key tile t (both monotone in q)
+      auto col_lo = [&](int t, int q) { return max(q - hw - ((int)p.k_pos0 + T.j0 + t * KT), 0); };
+      auto col_hi = [&](int t, int q) {
+        const int gk0 = (int)p.k_pos0 + T.j0 + t * KT;
+        return min(min(q - hw + p.w - 1 - gk0, T.len_b - 1 - gk0), KT - 1);
+      };
+      // Software pipeline over key tiles: A(t+1) (exponentials of S) runs while the
+      // tensor core computes P(t); B(t) then forms D(t).
+      for (int t = -1; t < nt; ++t) {
+        if (t + 1 < nt) {
+          // A: S(t+1) -> masked exponentials (kept packed), row sum L
+          const int u = t + 1, gg = gk + u, s = gg & 1;
+          const int clo = col_lo(u, gi), chi = col_hi(u, gi);
+          const int wlo = col_lo(u, gi_first), wlo_max = col_lo(u, gi_last);
+          const int whi_min = col_hi(u, gi_first), whi = col_hi(u, gi_last);
+          mbar_wait(bars + B_SFULL + s, (gg >> 1) & 1, a.status, 35);
+          tc_fence_after_sync();
+          if (u < 3) TRACEB(5 + 4 * u);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            const int c0 = PW * cq + 32 * c;
+            if (c0 + 31 < wlo || c0 > whi) {   // no row of this warp sees these 32 keys
+#pragma unroll
+              for (int j = 0; j < 16; ++j) En[16 * c + j] = 0u;
+              continue;
             }
-          } else {
+            float l0 = 0.f, l1 = 0.f;
+            const bool all_visible = c0 >= wlo_max && c0 + 31 <= whi_min;   // every row of this warp sees all 32 keys
             const unsigned span = (unsigned)(chi - clo);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
-              const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
-              const float e0 = ok0 ? ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co)) : 0.f;
-              const float e1 = ok1 ? ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co)) : 0.f;
-              l0 += e0;
-              l1 += e1;
-              En[16 * c + j] = pack_bf16(e0, e1);
+            for (int hc = 0; hc < 2; ++hc) {      // two halves of 16 columns keep the register footprint small
+              uint32_t rs[16];
+              tmem_ld16(lane_base + T_BUF + s * 128 + c0 + 16 * hc, rs);
+              tmem_ld_wait();
+              if (all_visible) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float e0 = ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co));
+                  const float e1 = ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co));
+                  l0 += e0;
+                  l1 += e1;
+                  En[16 * c + 8 * hc + j] = pack_bf16(e0, e1);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const int col = c0 + 16 * hc + 2 * j;
+                  const bool ok0 = chi >= clo && (unsigned)(col - clo) <= span;
+                  const bool ok1 = chi >= clo && (unsigned)(col + 1 - clo) <= span;
+                  const float e0 = ok0 ? ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co)) : 0.f;
+                  const float e1 = ok1 ? ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co)) : 0.f;
+                  l0 += e0;
+                  l1 += e1;
+                  En[16 * c + 8 * hc + j] = pack_bf16(e0, e1);
+                }
+              }
             }
+            L += l0 + l1;
           }
-          L += l0 + l1;
+          tc_fence_before_sync();
+          mbar_arrive(bars + B_ADONE + s);
+          if (u < 3) TRACEB(6 + 4 * u);
         }
-        tc_fence_before_sync();
-        mbar_arrive(a_done + s);
-        if (u < 3) TRACE(6 + 4 * u);
-      }
-      if (t >= 0) {
-        // B: P(t) -> D = E - P (packed bf16 into tensor memory), row sum dps
-        const int s = t & 1;
-        int clo, chi;
-        col_range(t, clo, chi);
-        const int wlo = __reduce_min_sync(0xffffffffu, clo), whi = __reduce_max_sync(0xffffffffu, chi);
-        const int wlo_max = __reduce_max_sync(0xffffffffu, clo), whi_min = __reduce_min_sync(0xffffffffu, chi);
-        mbar_wait(p_full + s, (t >> 1) & 1, a.status, 36);
-        if (t >= 1) mbar_wait(d_free, (t - 1) & 1, a.status, 37);
-        tc_fence_after_sync();
-        if (t < 3) TRACE(7 + 4 * t);
+        if (t >= 0) {
+          // B: P(t) -> D = E - P (packed bf16 into tensor memory), row sum dps
+          const int gg = gk + t, s = gg & 1;
+          const int clo = col_lo(t, gi), chi = col_hi(t, gi);
+          const int wlo = col_lo(t, gi_first), wlo_max = col_lo(t, gi_last);
+          const int whi_min = col_hi(t, gi_first), whi = col_hi(t, gi_last);
+          mbar_wait(bars + B_PFULL + s, (gg >> 1) & 1, a.status, 36);
+          if (gg >= 1) mbar_wait(bars + B_DFREE, (gg - 1) & 1, a.status, 37);
+          tc_fence_after_sync();
+          if (t < 3) TRACEB(7 + 4 * t);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const int c0 = PW * cq + 32 * c;
-          uint32_t dpk[16];
-          if (c0 + 31 < wlo || c0 > whi) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) dpk[j] = 0u;
-          } else {
-            uint32_t rp[32];
-            tmem_ld32(lane_base + T_BUF + s * 128 + c0, rp);
-            tmem_ld_wait();
+          for (int c = 0; c < CH; ++c) {
+            const int c0 = PW * cq + 32 * c;
+            const bool none_visible = c0 + 31 < wlo || c0 > whi;
+            const bool all_visible = c0 >= wlo_max && c0 + 31 <= whi_min;
+            const unsigned span = (unsigned)(chi - clo);
             float d0 = 0.f, d1 = 0.f;
-            if (c0 >= wlo_max && c0 + 31 <= whi_min) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float pv0 = __uint_as_float(rp[2 * j]), pv1 = __uint_as_float(rp[2 * j + 1]);
-                d0 += pv0;
-                d1 += pv1;
-                dpk[j] = pack_bf16(bf16_lo(Ec[16 * c + j]) - pv0, bf16_hi(Ec[16 * c + j]) - pv1);
-              }
-            } else {
-              const unsigned span = (unsigned)(chi - clo);
+            for (int hc = 0; hc < 2; ++hc) {
+              uint32_t dpk[8];
+              if (none_visible) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const bool ok0 = chi >= clo && (unsigned)(c0 + 2 * j - clo) <= span;
-                const bool ok1 = chi >= clo && (unsigned)(c0 + 2 * j + 1 - clo) <= span;
-                const float pv0 = ok0 ? __uint_as_float(rp[2 * j]) : 0.f;
-                const float pv1 = ok1 ? __uint_as_float(rp[2 * j + 1]) : 0.f;
-                d0 += pv0;
-                d1 += pv1;
-                dpk[j] = pack_bf16(bf16_lo(Ec[16 * c + j]) - pv0, bf16_hi(Ec[16 * c + j]) - pv1);
+                for (int j = 0; j < 8; ++j) dpk[j] = 0u;
+              } else {
+                uint32_t rp[16];
+                tmem_ld16(lane_base + T_BUF + s * 128 + c0 + 16 * hc, rp);
+                tmem_ld_wait();
+                if (all_visible) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const float pv0 = __uint_as_float(rp[2 * j]), pv1 = __uint_as_float(rp[2 * j + 1]);
+                    const uint32_t e = Ec[16 * c + 8 * hc + j];
+                    d0 += pv0;
+                    d1 += pv1;
+                    dpk[j] = pack_bf16(bf16_lo(e) - pv0, bf16_hi(e) - pv1);
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const int col = c0 + 16 * hc + 2 * j;
+                    const bool ok0 = chi >= clo && (unsigned)(col - clo) <= span;
+                    const bool ok1 = chi >= clo && (unsigned)(col + 1 - clo) <= span;
+                    const float pv0 = ok0 ? __uint_as_float(rp[2 * j]) : 0.f;
+                    const float pv1 = ok1 ? __uint_as_float(rp[2 * j + 1]) : 0.f;
+                    const uint32_t e = Ec[16 * c + 8 * hc + j];
+                    d0 += pv0;
+                    d1 += pv1;
+                    dpk[j] = pack_bf16(bf16_lo(e) - pv0, bf16_hi(e) - pv1);
+                  }
+                }
               }
+              tmem_st8(lane_base + T_D + c0 / 2 + 8 * hc, dpk);
             }
             dps += d0 + d1;
           }
-          tmem_st16(lane_base + T_D + c0 / 2, dpk);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          mbar_arrive(bars + B_BDONE + s);
+          if (t < 3) TRACEB(8 + 4 * t);
         }
-        tmem_st_wait();
-        tc_fence_before_sync();
-        mbar_arrive(b_done + s);
-        if (t < 3) TRACE(8 + 4 * t);
+#pragma unroll
+        for (int j = 0; j < 16 * CH; ++j) Ec[j] = En[j];
       }
+      // ---- combine the column groups of each row ----
+      s_xch[tid] = L;
+      s_xch[NSOFT + tid] = dps;
+      s_xch[2 * NSOFT + tid] = (z0 + z1) + (z2 + z3);
+      asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
+      float Z = 0.f;
+      L = 0.f;
+      dps = 0.f;
 #pragma unroll
-      for (int j = 0; j < 16 * CH; ++j) Ec[j] = En[j];
-    }
-    // ---- combine the column groups of each row ----
-    s_xch[tid] = L;
-    s_xch[NSOFT + tid] = dps;
-    s_xch[2 * NSOFT + tid] = (z0 + z1) + (z2 + z3);
-    asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
-    float Z = 0.f;
-    L = 0.f;
-    dps = 0.f;
-#pragma unroll
-    for (int j = 0; j < NCQ; ++j) {
-      const int m8 = (tid & 127) + 128 * j;
-      L += s_xch[m8];
-      dps += s_xch[NSOFT + m8];
-      Z += s_xch[2 * NSOFT + m8];
-    }
-    // ---- epilogue: this thread writes 64/NCQ of the row's 64 outputs ----
-    mbar_wait(bar_lr, 0, a.status, 38);
-    tc_fence_after_sync();
-    TRACE(20);
-    const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
-    constexpr int OW = 64 / NCQ;
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
-                          (int64_t)(i0 + row) * p.o_stride_t + OW * cq;
-    {
-      // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
-      uint32_t ro[16];
-      tmem_ld16(lane_base + T_O + OW * cq, ro);
-      tmem_ld_wait();
-      uint32_t o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
-      if (row < nq) {
-        reinterpret_cast<uint4*>(orow)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        reinterpret_cast<uint4*>(orow)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      for (int j = 0; j < NCQ; ++j) {
+        const int m8 = (tid & 127) + 128 * j;
+        L += s_xch[m8];
+        dps += s_xch[NSOFT + m8];
+        Z += s_xch[2 * NSOFT + m8];
       }
+      // ---- epilogue: this thread writes 64/NCQ of the row's 64 outputs ----
+      TRACEB(19);
+      mbar_wait(bars + B_DONE, it & 1, a.status, 38);
+      tc_fence_after_sync();
+      TRACEB(20);
+      const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + T.b * p.o_stride_b + T.h * p.o_stride_h +
+                            (int64_t)(T.i0 + row) * p.o_stride_t + OW * cq;
+      {
+        // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
+        uint32_t ro[16];
+        tmem_ld16(lane_base + T_O + OW * cq, ro);
+        tmem_ld_wait();
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
+        if (row < T.nq) {
+          reinterpret_cast<uint4*>(orow)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          reinterpret_cast<uint4*>(orow)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+      TRACEB(21);
+      // O has been read: the next query tile's phi(Q) arrival (B_PHIQ) releases the low-rank MMA that overwrites it
+      gk += nt;
     }
   }
-  if (tid == 0) TRACE(21);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == WP) {
@@ -1158,9 +1237,15 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   a.ksum = ksum;
   a.wmax = l.wmax;
   a.status = l.status;
+  a.ntq = (int)div_up(p.T, band::BQ);
+  a.ntiles = a.ntq * p.B * p.H;
   e = cudaFuncSetAttribute(tc_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band::SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  dim3 grid((unsigned)div_up(p.T, band::BQ), (unsigned)(p.B * p.H));
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  // persistent: one CTA per SM (shared and tensor memory allow no more), each walking its share of the query tiles
+  const unsigned grid = (unsigned)(a.ntiles < sms ? a.ntiles : sms);
   tc_band_kernel<<<grid, band::NTHREADS, band::SMEM_BYTES, st>>>(a);
   return cudaGetLastError();
 }
