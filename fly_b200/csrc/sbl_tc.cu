@@ -170,11 +170,13 @@ __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64
 __device__ long long g_trace[64][32];
 __device__ long long g_trace2[64][2][32];   // [cta][0 = producer, 1 = MMA issuer][slot]
 #define TRACE(slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (threadIdx.x == 0)) g_trace[blockIdx.y * 8 + blockIdx.x][slot] = clock64(); } while (0)
+#define TRACEC(cond, slot) do { if ((cond) && blockIdx.x < 64) g_trace[blockIdx.x][slot] = clock64(); } while (0)
 #define TRACEB(slot) do { if (it == 2 && blockIdx.x < 64 && threadIdx.x == 0) g_trace[blockIdx.x][slot] = clock64(); } while (0)
 #define TRACE2(who, slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (slot) < 32) g_trace2[blockIdx.y * 8 + blockIdx.x][who][slot] = clock64(); } while (0)
 #else
 #define TRACE(slot) do { } while (0)
 #define TRACEB(slot) do { } while (0)
+#define TRACEC(cond, slot) do { } while (0)
 #define TRACE2(who, slot) do { } while (0)
 #endif
 
@@ -642,13 +644,16 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     auto load_qw = [&](int it2) {
       if (it2 >= n_it) return;
       const BandTile T2 = band_tile(a, it2 * gridDim.x + blockIdx.x);
+      if (leader) TRACEC(it2 == 2, 22);
       if (it2 >= 1) mbar_wait(bars + B_QFREE, (it2 - 1) & 1, a.status, 20);
       if (leader) {
+        TRACEC(it2 == 2, 23);
         mbar_expect_tx(bars + B_Q, 16384);
         tma_load_4d(smem + OFF_Q, &a.tm_q, bars + B_Q, 0, T2.i0, T2.h, T2.b);
       }
       if (it2 >= 1) mbar_wait(bars + B_WFREE, (it2 - 1) & 1, a.status, 21);
       if (leader) {
+        TRACEC(it2 == 2, 24);
         mbar_expect_tx(bars + B_W, 16384);
         tma_load_2d(smem + OFF_KV, &a.tm_w, bars + B_W, 0, 0);
       }
@@ -746,11 +751,15 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
       const int nt = T.nt;
       // U = Q Wt^T into the buffer of key tile gk+1; that buffer last held key tile gk-1
+      if (leader) TRACEC(it == 2, 25);
       mbar_wait(bars + B_Q, it & 1, a.status, 30);
+      if (leader) TRACEC(it == 2, 26);
       mbar_wait(bars + B_W, it & 1, a.status, 30);
+      if (leader) TRACEC(it == 2, 27);
       if (gk >= 1) b_done_wait(gk - 1);
       tc_fence_after_sync();
       if (leader) {
+        TRACEC(it == 2, 28);
         const uint32_t td = tb + T_BUF + ((gk + 1) & 1) * 128;
         mma_ss(td, dQ, dKV, id_n128, false);
         mma_ss(td, dQ + 2, dKV + 2, id_n128, true);
