@@ -12,6 +12,7 @@ from . import build as _build
 
 SBL_DTYPE_F32 = 0
 SBL_DTYPE_BF16 = 1
+SBL_FLAG_GENERIC_PATH = 1
 
 SBL_OK = 0
 SBL_ERR_INVALID_ARGUMENT = -1
@@ -24,7 +25,7 @@ ABI_VERSION = 1
 
 EXPORTS = ('sbl_version', 'sbl_last_error', 'sbl_has_tensor_path', 'sbl_workspace_bytes', 'sbl_forward',
            'sbl_key_logscale', 'sbl_key_summary', 'sbl_band_forward', 'sbl_query_features',
-           'sbl_key_features', 'sbl_check_status', 'sbl_key_logscale_static', 'sbl_static_last_error')
+           'sbl_key_features', 'sbl_attention_weights', 'sbl_check_status', 'sbl_key_logscale_static', 'sbl_static_last_error')
 
 
 class SblParams(ctypes.Structure):
@@ -50,7 +51,8 @@ class SblParams(ctypes.Structure):
         ('q_pos0', ctypes.c_int64), ('k_pos0', ctypes.c_int64),
         ('S_total', ctypes.c_int64),
         ('sum_lo', ctypes.c_int32), ('sum_hi', ctypes.c_int32),
-        ('reserved', ctypes.c_int32 * 4),
+        ('flags', ctypes.c_int32),
+        ('reserved', ctypes.c_int32 * 3),
     ]
 
 
@@ -106,6 +108,8 @@ def load():
         lib.sbl_query_features.argtypes = [P, vp, sz, vp, vp, vp]
         lib.sbl_key_features.restype = ctypes.c_int
         lib.sbl_key_features.argtypes = [P, vp, sz, vp, vp, vp]
+        lib.sbl_attention_weights.restype = ctypes.c_int
+        lib.sbl_attention_weights.argtypes = [P, vp, sz, vp, vp, vp, vp]
         lib.sbl_check_status.restype = ctypes.c_int
         lib.sbl_check_status.argtypes = [P, vp, sz, vp]
         lib.sbl_key_logscale_static.restype = ctypes.c_int

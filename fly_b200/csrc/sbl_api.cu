@@ -43,7 +43,8 @@ int validate(const SblParams* p) {
   if (p->D > 128) return fail(SBL_ERR_UNSUPPORTED, "value dim D=%d > 128 has no kernel", p->D);
   if ((int64_t)p->B * p->H > 65535)
     return fail(SBL_ERR_UNSUPPORTED, "B*H=%lld exceeds the grid limit 65535", (long long)p->B * p->H);
-  for (int i = 0; i < 4; ++i)
+  if (p->flags & ~SBL_FLAG_GENERIC_PATH) return fail(SBL_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", p->flags);
+  for (int i = 0; i < 3; ++i)
     if (p->reserved[i] != 0) return fail(SBL_ERR_INVALID_ARGUMENT, "reserved fields must be 0");
   if (p->S_total <= 0 || p->q_pos0 < 0 || p->k_pos0 < 0)
     return fail(SBL_ERR_INVALID_ARGUMENT, "S_total must be positive and q_pos0/k_pos0 non-negative");
@@ -93,7 +94,7 @@ int check_device_status(const Workspace& ws, char* base, cudaStream_t st) {
 
 bool plan_workspace(const SblParams& p, Workspace* ws, const char** why) {
   const size_t BH = (size_t)p.B * p.H, m = 2 * (size_t)p.r;
-  ws->tensor = tc_supported(p);
+  ws->tensor = tc_supported(p) && !(p.flags & SBL_FLAG_GENERIC_PATH);
   // split the summary over key rows: at most 64 splits, at least 256 rows each
   const int rows = p.sum_hi - p.sum_lo;
   int split_rows = 256;
@@ -118,6 +119,7 @@ bool plan_workspace(const SblParams& p, Workspace* ws, const char** why) {
   ws->kv = off;      off = align_up(off + BH * m * p.D * 4);
   ws->ksum = off;    off = align_up(off + BH * m * 4);
   ws->partial = off; off = align_up(off + BH * ws->nsplit * m * (ws->tensor ? 80 : p.D + 1) * 4);
+  ws->lognorm = off; off = align_up(off + (ws->tensor ? 0 : BH * p.T * 4));
   ws->status = off;  off = align_up(off + 64);
   ws->total = off;
   (void)why;
@@ -243,6 +245,23 @@ int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, voi
                               reinterpret_cast<float*>(base + ws.qls), st)) != cudaSuccess)
     return cuda_fail(e, "query features");
   if ((e = f32_band(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "band forward");
+  return SBL_OK;
+}
+
+int sbl_attention_weights(const SblParams* p, void* workspace, size_t workspace_bytes, float* attn,
+                          float* attn_unnorm, float* attn_lr_unnorm, void* cuda_stream) {
+  Workspace ws;
+  int rc = prepare(p, workspace, workspace_bytes, &ws);
+  if (rc != SBL_OK) return rc;
+  if (!attn) return fail(SBL_ERR_INVALID_ARGUMENT, "attn is null");
+  if (ws.tensor)
+    return fail(SBL_ERR_INVALID_ARGUMENT, "sbl_attention_weights needs SBL_FLAG_GENERIC_PATH in this and the forward call");
+  if (p->q_pos0 != 0 || p->k_pos0 != 0 || p->S_total != p->S)
+    return fail(SBL_ERR_UNSUPPORTED, "dense attention weights are not built for sequence shards");
+  char* base = static_cast<char*>(workspace);
+  cudaError_t e = f32_attention_weights(*p, ws, base, reinterpret_cast<const float*>(base + ws.beta), attn, attn_unnorm,
+                                        attn_lr_unnorm, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "attention weights");
   return SBL_OK;
 }
 

@@ -23,6 +23,7 @@ struct Workspace {
   size_t kv;        // (B,H,m,D) fp32
   size_t ksum;      // (B,H,m) fp32
   size_t partial;   // split-S partial summaries
+  size_t lognorm;   // generic path: log_normalization per query row (B,H,T) fp32
   size_t status;    // int32[4] device status words, then small scalars
   size_t total;
   int nsplit;       // number of S splits of the summary GEMM
@@ -49,6 +50,9 @@ cudaError_t f32_query_features(const SblParams& p, const Workspace& ws, char* ba
                                float* qls_out, cudaStream_t st);
 cudaError_t f32_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
                      const float* kv, const float* ksum, cudaStream_t st);
+
+cudaError_t f32_attention_weights(const SblParams& p, const Workspace& ws, char* base, const float* beta,
+                                  float* attn, float* attn_un, float* attn_lr, cudaStream_t st);
 
 // ---- tensor-core path (bf16 storage, tcgen05 + TMA), sbl_tc.cu ----
 bool tc_supported(const SblParams& p);

@@ -67,6 +67,9 @@ __device__ __forceinline__ void tile_nt(float (&acc)[4][4], const TA* A, int64_t
       fetch_slice(ra, A, lda, na, k0 + KS, K);
       fetch_slice(rb, B, ldb, nb, k0 + KS, K);
     }
+    // two-level sum: one partial per K slice, so the rounding error grows with K/16, not K
+    // (the feature dimension can be tens of thousands)
+    float part[4][4] = {};
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       const float4 a = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
@@ -76,8 +79,12 @@ __device__ __forceinline__ void tile_nt(float (&acc)[4][4], const TA* A, int64_t
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(av[i], bv[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
   }
 }
 
@@ -251,6 +258,7 @@ summary_partial_kernel(const float* phik, const void* vptr, int64_t sb, int64_t 
       sB[kk][c] = !in ? 0.f : (d < D ? ldf(v + (int64_t)s * ss + d) : (d == D ? 1.f : 0.f));
     }
     __syncthreads();
+    float part[4][4] = {};   // two-level sum over the keys
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       const float4 a4 = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
@@ -260,8 +268,12 @@ summary_partial_kernel(const float* phik, const void* vptr, int64_t sb, int64_t 
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(av[i], bv[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
   }
   float* out = partial + ((int64_t)bh * gridDim.y + blockIdx.y) * m * D1;
 #pragma unroll
@@ -305,7 +317,7 @@ __global__ void summary_combine_kernel(const float* partial, int nsplit, int m, 
 template <typename T, int DV>
 __global__ void __launch_bounds__(NTHR)
 band_kernel(SblParams p, const float* phiq, const float* qls, const float* phik, const float* beta,
-            const float* kv, const float* ksum) {
+            const float* kv, const float* ksum, float* lognorm) {
   constexpr int DVW = DV * 16;
   extern __shared__ __align__(16) float smem[];
   float(*sA)[LDT] = reinterpret_cast<float(*)[LDT]>(smem);
@@ -425,6 +437,11 @@ band_kernel(SblParams p, const float* phiq, const float* qls, const float* phik,
     }
     if (threadIdx.x < KS) sKs[threadIdx.x] = (f0 + threadIdx.x < m) ? ksb[f0 + threadIdx.x] : 0.f;
     __syncthreads();
+    float zp[4] = {0.f, 0.f, 0.f, 0.f}, lp[4][DV];   // two-level sums over the features
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int d = 0; d < DV; ++d) lp[i][d] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       const float4 a4 = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
@@ -435,10 +452,16 @@ band_kernel(SblParams p, const float* phiq, const float* qls, const float* phik,
       for (int d = 0; d < DV; ++d) vv[d] = sV[kk * DVW + tx + 16 * d];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        Z[i] = fmaf(av[i], ks, Z[i]);
+        zp[i] = fmaf(av[i], ks, zp[i]);
 #pragma unroll
-        for (int d = 0; d < DV; ++d) olr[i][d] = fmaf(av[i], vv[d], olr[i][d]);
+        for (int d = 0; d < DV; ++d) lp[i][d] = fmaf(av[i], vv[d], lp[i][d]);
       }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      Z[i] += zp[i];
+#pragma unroll
+      for (int d = 0; d < DV; ++d) olr[i][d] += lp[i][d];
     }
   }
 
@@ -454,6 +477,7 @@ band_kernel(SblParams p, const float* phiq, const float* qls, const float* phik,
     const float hi = fmaxf(lse, lrn), lo = fminf(lse, lrn);
     const float n = hi + log1pf(expf(lo - hi));  // logaddexp; lo = -inf gives hi
     const float ce = expf(c[i] - n), ps = expf(pls - n);
+    if (tx == 0) lognorm[(int64_t)bh * p.T + i0 + row] = n;
 #pragma unroll
     for (int d = 0; d < DV; ++d) {
       const int col = tx + 16 * d;
@@ -462,25 +486,73 @@ band_kernel(SblParams p, const float* phiq, const float* qls, const float* phik,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Dense attention matrices of the need_weights branch (sblocal_attention.py:124-136).  One block =
+// 64 queries x 64 keys of one (b,h): low-rank part phi(q).phi(k) for every pair, exact part only
+// inside the window and key length.
+template <typename T>
+__global__ void __launch_bounds__(NTHR)
+weights_kernel(SblParams p, const float* phiq, const float* qls, const float* phik, const float* beta,
+               const float* lognorm, float* attn, float* attn_un, float* attn_lr) {
+  __shared__ __align__(16) float sA[KS][LDT];
+  __shared__ __align__(16) float sB[KS][LDT];
+  const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+  const int bh = blockIdx.z, b = bh / p.H, h = bh % p.H;
+  const int i0 = blockIdx.y * TILE, s0 = blockIdx.x * TILE;
+  const int nq = min(TILE, p.T - i0), nk = min(TILE, p.S - s0);
+  const int m = 2 * p.r, hw = p.w / 2;
+  int64_t len_b = p.key_lengths ? p.key_lengths[b] : p.S_total;
+  const T* q = reinterpret_cast<const T*>(p.q) + b * p.q_stride_b + h * p.q_stride_h + (int64_t)i0 * p.q_stride_t;
+  const T* k = reinterpret_cast<const T*>(p.k) + b * p.k_stride_b + h * p.k_stride_h + (int64_t)s0 * p.k_stride_s;
+  float sacc[4][4] = {}, pacc[4][4] = {};
+  tile_nt(sacc, q, p.q_stride_t, nq, k, p.k_stride_s, nk, p.E, sA, sB);
+  tile_nt(pacc, phiq + ((int64_t)bh * p.T + i0) * m, (int64_t)m, nq, phik + ((int64_t)bh * p.S + s0) * m, (int64_t)m,
+          nk, m, sA, sB);
+  const float beta_bh = beta[bh];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = ty * 4 + i;
+    if (row >= nq) continue;
+    const int gi = i0 + row;
+    const float n = lognorm[(int64_t)bh * p.T + gi];
+    const float pls = qls[(int64_t)bh * p.T + gi] + beta_bh;
+    const float ps = expf(pls - n), en = expf(n), epls = expf(pls);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = tx * 4 + j;
+      if (col >= nk) continue;
+      const int gk = s0 + col;
+      const bool in_win = gk >= gi - hw && gk <= gi - hw + p.w - 1 && gk < len_b;
+      const float lr = pacc[i][j];   // phi(K) is zero at padded keys already
+      const float local = in_win ? expf(p.softmax_temp * sacc[i][j] - n) - lr * ps : 0.f;
+      const float a = local + lr * ps;
+      const int64_t o = (((int64_t)bh * p.T + gi) * p.S) + gk;
+      attn[o] = a;
+      if (attn_un) attn_un[o] = a * en;
+      if (attn_lr) attn_lr[o] = lr * epls;
+    }
+  }
+}
+
 template <typename T, int DV>
 cudaError_t launch_band(const SblParams& p, const float* phiq, const float* qls, const float* phik,
-                        const float* beta, const float* kv, const float* ksum, cudaStream_t st) {
+                        const float* beta, const float* kv, const float* ksum, float* lognorm, cudaStream_t st) {
   const size_t smem = sizeof(float) * (2 * KS * LDT + 2 * TILE * (TILE + 1) + TILE * DV * 16 + KS);
   cudaError_t e = cudaFuncSetAttribute(band_kernel<T, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)div_up(p.T, TILE), (unsigned)(p.B * p.H));
-  band_kernel<T, DV><<<grid, NTHR, smem, st>>>(p, phiq, qls, phik, beta, kv, ksum);
+  band_kernel<T, DV><<<grid, NTHR, smem, st>>>(p, phiq, qls, phik, beta, kv, ksum, lognorm);
   return cudaGetLastError();
 }
 
 template <typename T>
 cudaError_t launch_band_t(const SblParams& p, const float* phiq, const float* qls, const float* phik,
-                          const float* beta, const float* kv, const float* ksum, cudaStream_t st) {
+                          const float* beta, const float* kv, const float* ksum, float* lognorm, cudaStream_t st) {
   const int dv = (int)div_up(p.D, 16);
-  if (dv <= 1) return launch_band<T, 1>(p, phiq, qls, phik, beta, kv, ksum, st);
-  if (dv <= 2) return launch_band<T, 2>(p, phiq, qls, phik, beta, kv, ksum, st);
-  if (dv <= 4) return launch_band<T, 4>(p, phiq, qls, phik, beta, kv, ksum, st);
-  return launch_band<T, 8>(p, phiq, qls, phik, beta, kv, ksum, st);
+  if (dv <= 1) return launch_band<T, 1>(p, phiq, qls, phik, beta, kv, ksum, lognorm, st);
+  if (dv <= 2) return launch_band<T, 2>(p, phiq, qls, phik, beta, kv, ksum, lognorm, st);
+  if (dv <= 4) return launch_band<T, 4>(p, phiq, qls, phik, beta, kv, ksum, lognorm, st);
+  return launch_band<T, 8>(p, phiq, qls, phik, beta, kv, ksum, lognorm, st);
 }
 
 FeatArgs feat_args(const SblParams& p, const Workspace& ws, char* base, bool query) {
@@ -581,13 +653,28 @@ cudaError_t f32_query_features(const SblParams& p, const Workspace& ws, char* ba
   return launch_feat<MODE_QUERY>(p, a, st);
 }
 
+cudaError_t f32_attention_weights(const SblParams& p, const Workspace& ws, char* base, const float* beta,
+                                  float* attn, float* attn_un, float* attn_lr, cudaStream_t st) {
+  const float* phiq = reinterpret_cast<const float*>(base + ws.phiq);
+  const float* qls = reinterpret_cast<const float*>(base + ws.qls);
+  const float* phik = reinterpret_cast<const float*>(base + ws.phik);
+  const float* lognorm = reinterpret_cast<const float*>(base + ws.lognorm);
+  dim3 grid((unsigned)div_up(p.S, TILE), (unsigned)div_up(p.T, TILE), (unsigned)(p.B * p.H));
+  if (p.dtype == SBL_DTYPE_F32)
+    weights_kernel<float><<<grid, NTHR, 0, st>>>(p, phiq, qls, phik, beta, lognorm, attn, attn_un, attn_lr);
+  else
+    weights_kernel<__nv_bfloat16><<<grid, NTHR, 0, st>>>(p, phiq, qls, phik, beta, lognorm, attn, attn_un, attn_lr);
+  return cudaGetLastError();
+}
+
 cudaError_t f32_band(const SblParams& p, const Workspace& ws, char* base, const float* beta, const float* kv,
                      const float* ksum, cudaStream_t st) {
   const float* phiq = reinterpret_cast<const float*>(base + ws.phiq);
   const float* qls = reinterpret_cast<const float*>(base + ws.qls);
   const float* phik = reinterpret_cast<const float*>(base + ws.phik);
-  if (p.dtype == SBL_DTYPE_F32) return launch_band_t<float>(p, phiq, qls, phik, beta, kv, ksum, st);
-  return launch_band_t<__nv_bfloat16>(p, phiq, qls, phik, beta, kv, ksum, st);
+  float* lognorm = reinterpret_cast<float*>(base + ws.lognorm);
+  if (p.dtype == SBL_DTYPE_F32) return launch_band_t<float>(p, phiq, qls, phik, beta, kv, ksum, lognorm, st);
+  return launch_band_t<__nv_bfloat16>(p, phiq, qls, phik, beta, kv, ksum, lognorm, st);
 }
 
 }  // namespace sbl

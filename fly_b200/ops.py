@@ -20,7 +20,7 @@ class Problem:
     alive for as long as the block is used)."""
 
     def __init__(self, query, key, value, W, local_context, softmax_temp=None, softmax_eps=0.0,
-                 key_lengths=None, out=None, q_pos0=0, k_pos0=0, S_total=None, sum_range=None):
+                 key_lengths=None, out=None, q_pos0=0, k_pos0=0, S_total=None, sum_range=None, generic=False):
         if not (query.is_cuda and key.is_cuda and value.is_cuda):
             raise ValueError('sblocal_b200 runs on CUDA tensors only (there is no CPU path)')
         if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:
@@ -68,6 +68,7 @@ class Problem:
         p.q_pos0, p.k_pos0 = int(q_pos0), int(k_pos0)
         p.S_total = int(S_total) if S_total is not None else S
         p.sum_lo, p.sum_hi = sum_range if sum_range is not None else (0, S)
+        p.flags = _cabi.SBL_FLAG_GENERIC_PATH if generic else 0
         self.params = p
         self.device = dev
         self.out = out
@@ -127,6 +128,18 @@ class Problem:
         self._call(_cabi.load().sbl_band_forward, beta.data_ptr(), kv.data_ptr(), ksum.data_ptr(),
                    workspace=workspace)
         return self.out
+
+    def attention_weights(self, unnormalized=False, workspace=None):
+        """Dense (B,H,T,S) attention matrix (and, with `unnormalized`, the two
+        unnormalised matrices) of the forward just run on this workspace; the
+        problem must have been created with generic=True."""
+        B, H, T, S = self.shape[:4]
+        mk = lambda: torch.empty(B, H, T, S, device=self.device, dtype=torch.float32)
+        attn = mk()
+        un, lr = (mk(), mk()) if unnormalized else (None, None)
+        self._call(_cabi.load().sbl_attention_weights, attn.data_ptr(), un.data_ptr() if unnormalized else None,
+                   lr.data_ptr() if unnormalized else None, workspace=workspace)
+        return (attn, un, lr) if unnormalized else attn
 
     def query_features(self):
         B, H, T = self.shape[:3]

@@ -7,7 +7,7 @@ hand-written sm_100a CUDA kernels behind the C ABI of include/sblocal_b200.h.
 Forward only.  There is no CPU path: CPU tensors raise.  Not built (raise
 NotImplementedError): causal=True (the reference marks it unchecked, :61),
 an attn_mask that masks anything (the reference's own assert at :106 rejects
-it), dropout in training mode, need_weights.
+it), dropout in training mode.
 """
 import torch
 import torch.nn as nn
@@ -53,8 +53,6 @@ class SBLocalAttention(nn.Module):
         (out (B,T,H,D), None)."""
         if self.causal:
             raise NotImplementedError('causal SBLocal attention is not built')
-        if need_weights or return_attn_unnormalized:
-            raise NotImplementedError('need_weights (dense T x S attention output) is not built')
         if self.training and self.dropout.p > 0:
             raise NotImplementedError('attention dropout in training mode is not built')
         if attn_mask is not None and not bool(attn_mask.all_ones):
@@ -65,6 +63,14 @@ class SBLocalAttention(nn.Module):
         self.feature_map.new_feature_map(query.device)
         W = self.feature_map.projection_matrix
         args = (query, key, value, W, self.local_context, self.softmax_temp, self.softmax_eps, key_lengths)
+        if need_weights:
+            # dense (B,H,T,S) matrices, fp32 (sblocal_attention.py:124-136): the generic kernels keep phi(Q) and
+            # phi(K) in the workspace for this; meant for tests and inspection, O(T*S) memory
+            prob = ops.Problem(*args, generic=True)
+            ws = prob.workspace()
+            out = prob.forward(workspace=ws)
+            attn = prob.attention_weights(unnormalized=return_attn_unnormalized, workspace=ws)
+            return out, attn
         if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
             out = _ForwardOnly.apply(*args)
         else:

@@ -36,6 +36,10 @@ typedef enum SblStatus {
 
 typedef enum SblDType { SBL_DTYPE_F32 = 0, SBL_DTYPE_BF16 = 1 } SblDType;
 
+/* Run the generic fp32-math kernels even where the bf16 tensor-core kernels apply (needed by
+ * sbl_attention_weights, which reads the fp32 phi(Q)/phi(K) those kernels leave in the workspace). */
+#define SBL_FLAG_GENERIC_PATH 1
+
 /*
  * One problem description shared by all entry points.
  *
@@ -69,7 +73,8 @@ typedef struct SblParams {
   int64_t q_pos0, k_pos0;     /* global positions of buffer row 0                          */
   int64_t S_total;            /* global number of keys                                     */
   int32_t sum_lo, sum_hi;     /* key buffer rows that enter this rank's summary            */
-  int32_t reserved[4];        /* must be 0                                                 */
+  int32_t flags;              /* SBL_FLAG_* bits                                           */
+  int32_t reserved[3];        /* must be 0                                                 */
 } SblParams;
 
 /* ABI version (SBL_ABI_VERSION of the built library). */
@@ -124,6 +129,17 @@ int sbl_key_summary(const SblParams* p, void* workspace, size_t workspace_bytes,
  */
 int sbl_band_forward(const SblParams* p, void* workspace, size_t workspace_bytes, const float* beta,
                      const float* kv, const float* ksum, void* cuda_stream);
+
+/*
+ * Dense attention matrices of the need_weights / return_attn_unnormalized branch
+ * (sblocal_attention.py:124-136), for tests and inspection: O(T*S) memory.  Call after sbl_forward (or
+ * the three stages) on the same workspace with SBL_FLAG_GENERIC_PATH set in both calls.
+ *   attn            (B,H,T,S) fp32: banded weights scattered into the dense matrix + phi(Q)phi(K)^T * prime_scale
+ *   attn_unnorm     attn * exp(log_normalization)                     (null to skip)
+ *   attn_lr_unnorm  phi(Q)phi(K)^T * exp(prime_log_scale)             (null to skip)
+ */
+int sbl_attention_weights(const SblParams* p, void* workspace, size_t workspace_bytes, float* attn,
+                          float* attn_unnorm, float* attn_lr_unnorm, void* cuda_stream);
 
 /*
  * Synchronises the stream and reports whether any kernel of the preceding

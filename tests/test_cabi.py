@@ -73,6 +73,7 @@ def test_workspace_size_is_reported(sbl_lib):
     (dict(sum_hi=101), -1, 'summary rows'),
     (dict(k_pos0=10, S_total=200), -1, 'halo'),
     (dict(S_total=50), -1, 'exceed S_total'),
+    (dict(flags=6), -1, 'flag'),
 ])
 def test_bad_arguments_are_rejected_with_a_message(sbl_lib, over, code, fragment):
     rc, _ = _bytes(sbl_lib, _params(**over))

@@ -65,7 +65,7 @@ def test_unbuilt_options_raise():
     q = torch.randn(1, 5, 1, 8)
     with pytest.raises(NotImplementedError):
         SBLocalAttention(4, 8, 8, causal=True)(q, q, q)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match='CUDA'):
         SBLocalAttention(4, 8, 8).eval()(q, q, q, need_weights=True)
     with pytest.raises(NotImplementedError):
         SBLocalAttention(4, 8, 8, attention_dropout=0.1).train()(q, q, q)
@@ -100,7 +100,24 @@ def test_package_exports():
 
 def test_dropin_registers_the_reference_module_path():
     import importlib
+    import sys
     from fly_b200 import dropin
+    saved = {k: sys.modules.get(k) for k in ('src', 'src.models', 'src.models.attention', dropin.TARGET)}
+    try:
+        _check_dropin(dropin, importlib)
+    finally:
+        # leave the interpreter as found: other tests import the reference's own module under this name
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+        parent = sys.modules.get('src.models.attention')
+        if parent is not None and saved[dropin.TARGET] is None and hasattr(parent, 'sblocal_attention'):
+            delattr(parent, 'sblocal_attention')
+
+
+def _check_dropin(dropin, importlib):
     dropin.install()
     mod = importlib.import_module('src.models.attention.sblocal_attention')
     assert mod.SBLocalAttention is SBLocalAttention
