@@ -590,10 +590,30 @@ __device__ __forceinline__ BandTile band_tile(const BandArgs& a, int tile_id) {
   return t;
 }
 
-// Persistent: CTA c processes query tiles c, c + gridDim.x, ...  Key tiles are numbered
-// globally per CTA (g = 0, 1, ... across query tiles); key tile g uses accumulator buffer g & 1 and
-// phi(K) slot g & 1, and the U of a query tile goes to the buffer its second key tile will use,
-// so that the next query tile's Q/Wt loads and U = Q Wt^T overlap the current tile's tail.
+// Which phi(K) tile each of the two shared-memory slots holds.  Key tile kt of a (b,h) lives in slot
+// kt & 1; consecutive query tiles of a run share two of their three key tiles, so only the new one is
+// loaded.  The producer and the P-issuing warp walk the same sequence and keep identical copies.
+struct PkTrack {
+  int bh0 = -1, bh1 = -1, kt0 = -1, kt1 = -1;
+  int fills0 = 0, fills1 = 0;   // completed or pending loads per slot
+  int uses0 = 0, uses1 = 0;     // P products issued (or planned) per slot
+  __device__ bool resident(int slot, int b, int k) const {
+    return slot ? (bh1 == b && kt1 == k) : (bh0 == b && kt0 == k);
+  }
+  __device__ int fills(int slot) const { return slot ? fills1 : fills0; }
+  __device__ int uses(int slot) const { return slot ? uses1 : uses0; }
+  __device__ void filled(int slot, int b, int k) {
+    if (slot) { bh1 = b; kt1 = k; ++fills1; } else { bh0 = b; kt0 = k; ++fills0; }
+  }
+  __device__ void used(int slot) {
+    if (slot) ++uses1; else ++uses0;
+  }
+};
+
+// Persistent: CTA c processes a run of consecutive query tiles.  Key tiles are numbered
+// per CTA (g = 0, 1, ... across query tiles); key tile g uses accumulator buffer g & 1, and the U of a
+// query tile goes to the buffer its second key tile will use, so that the next query tile's Q/Wt loads
+// and U = Q Wt^T overlap the current tile's tail.
 __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_constant__ BandArgs a) {
   using namespace band;
   extern __shared__ uint8_t smem_raw[];
@@ -606,7 +626,9 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int hw = p.w / 2;
-  const int n_it = (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // query tiles of this CTA
+  // this CTA's run of consecutive query tiles: neighbours in a run share two of their three key tiles
+  const int tile_lo = (int)((int64_t)a.ntiles * blockIdx.x / gridDim.x);
+  const int n_it = (int)((int64_t)a.ntiles * (blockIdx.x + 1) / gridDim.x) - tile_lo;
 
   if (warp == WP + 1) {
     if (lane < B_COUNT) {
@@ -639,11 +661,12 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       prefetch_tmap(&a.tm_kv);
     }
     int gk = 0;   // key tiles loaded so far
+    PkTrack pk;
     // Q and Wt of query tile `it2`: issued as soon as the previous tile has released the two buffers,
     // i.e. in the middle of the previous tile, so that U = Q Wt^T of the next tile is ready at its start
     auto load_qw = [&](int it2) {
       if (it2 >= n_it) return;
-      const BandTile T2 = band_tile(a, it2 * gridDim.x + blockIdx.x);
+      const BandTile T2 = band_tile(a, tile_lo + it2);
       if (leader) TRACEC(it2 == 2, 22);
       if (it2 >= 1) mbar_wait(bars + B_QFREE, (it2 - 1) & 1, a.status, 20);
       if (leader) {
@@ -660,7 +683,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     };
     load_qw(0);
     for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      const BandTile T = band_tile(a, tile_lo + it);
       // K and V are single-buffered, phi(K) double-buffered.  Issue order follows the order
       // in which the tensor core frees the buffers: K(g), phi(K)(g), then V(g-1).
       auto load_v = [&](int t) {
@@ -686,12 +709,21 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           mbar_expect_tx(bars + B_KFULL, 16384);
           tma_load_4d(smem + OFF_K, &a.tm_k, bars + B_KFULL, 0, row0, T.h, T.b);
         }
-        if (g >= 2) mbar_wait(bars + B_PKEMPTY + s, ((g >> 1) - 1) & 1, a.status, 22);
-        if (leader) {
-          mbar_expect_tx(bars + B_PKFULL + s, 65536);
+        {
+          const int kt = row0 / KT, ps = kt & 1;
+          if (!pk.resident(ps, T.bh, kt)) {
+            // every P that read the slot's old tile must be done: wait for the latest of them
+            if (pk.uses(ps) >= 1) mbar_wait(bars + B_PKEMPTY + ps, (pk.uses(ps) - 1) & 1, a.status, 22);
+            if (leader) {
+              mbar_expect_tx(bars + B_PKFULL + ps, 65536);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            tma_load_3d(smem + OFF_PK + s * 65536 + j * 16384, &a.tm_phik, bars + B_PKFULL + s, j * 64, row0, T.bh);
+              for (int j = 0; j < 4; ++j)
+                tma_load_3d(smem + OFF_PK + ps * 65536 + j * 16384, &a.tm_phik, bars + B_PKFULL + ps, j * 64, row0,
+                            T.bh);
+            }
+            pk.filled(ps, T.bh, kt);
+          }
+          pk.used(ps);
         }
         if (t == 0) {
           load_v(0);
@@ -748,7 +780,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       __syncwarp();
     };
     for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      const BandTile T = band_tile(a, tile_lo + it);
       const int nt = T.nt;
       // U = Q Wt^T into the buffer of key tile gk+1; that buffer last held key tile gk-1
       if (leader) TRACEC(it == 2, 25);
@@ -807,21 +839,27 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
     const uint64_t dPK0 = smem_desc_sw128(smem_u32(smem + OFF_PK), 16, 1024);
     int gk = 0;
+    PkTrack pk;
     for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      const BandTile T = band_tile(a, tile_lo + it);
       mbar_wait(bars + B_PHIQ, it & 1, a.status, 39);
       for (int t = 0; t < T.nt; ++t) {
         const int g = gk + t, s = g & 1;
+        const int kt = T.j0 / KT + t, ps = kt & 1;
         mbar_wait(bars + B_ADONE + s, (g >> 1) & 1, a.status, 26);
-        mbar_wait(bars + B_PKFULL + s, (g >> 1) & 1, a.status, 27);
+        if (!pk.resident(ps, T.bh, kt)) {   // a tile still resident from the previous query tile was waited for then
+          mbar_wait(bars + B_PKFULL + ps, pk.fills(ps) & 1, a.status, 27);
+          pk.filled(ps, T.bh, kt);
+        }
+        pk.used(ps);
         tc_fence_after_sync();
         if (leader) {
-          const uint64_t dPK = dPK0 + (uint64_t)(s * (65536 >> 4));
+          const uint64_t dPK = dPK0 + (uint64_t)(ps * (65536 >> 4));
           const uint32_t td = tb + T_BUF + s * 128;
 #pragma unroll
           for (int k = 0; k < 16; ++k)
             mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
-          mma_commit(bars + B_PKEMPTY + s);
+          mma_commit(bars + B_PKEMPTY + ps);
           mma_commit(bars + B_PFULL + s);
         }
         __syncwarp();
@@ -840,7 +878,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     const float sc = p.softmax_temp * kLog2e;
     int gk = 0;
     for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, it * gridDim.x + blockIdx.x);
+      const BandTile T = band_tile(a, tile_lo + it);
       const int nt = T.nt;
       const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
       const int gi_first = (int)p.q_pos0 + T.i0 + qd * 32, gi_last = gi_first + 31;   // rows of this warp
