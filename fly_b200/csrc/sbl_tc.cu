@@ -196,15 +196,18 @@ struct KeysArgs {
 
 namespace keys {
 constexpr int TILE = 128;
-constexpr int NFEAT = 256;                 // feature threads: warps 0-7; warp w owns key rows 32*(w%4).., projection half w/4
-constexpr int NTHREADS = NFEAT + 64;       // + producer warp 8 + MMA warp 9
+constexpr int NFQ = 2;                     // projection groups per key row: a feature thread owns 128/NFQ projections
+constexpr int NFEAT = 128 * NFQ;           // feature threads: warp w owns key rows 32*(w%4).., projection group w/4
+constexpr int CHK = 4 / NFQ;               // 32-projection chunks per thread
+constexpr int WPK = NFEAT / 32;            // producer warp; WPK+1: MMA warp
+constexpr int NTHREADS = NFEAT + 64;
 constexpr uint32_t OFF_W = 0;                    // 16 KB  [128 r][64 e]
 constexpr uint32_t OFF_K = 16384;                // ring of [128 keys][64 e] tiles, 16 KB each: 2 deep (4 deep in the beta pass)
 constexpr uint32_t OFF_V = 49152;                // 2 x 16 KB V tiles; [V | 1] is one MN-major operand (N = 80) whose second
 constexpr uint32_t OFF_ONES = OFF_V + 32768;     // 64-column block is this 16 KB block of ones (leading offset per V slot)
 constexpr uint32_t OFF_A = OFF_ONES + 16384;     // 2 x 64 KB: 4 blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
 constexpr uint32_t OFF_BAR = OFF_A + 2 * 65536;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;    // + alignment slack
+constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;    // + alignment slack
 // tensor memory columns
 constexpr uint32_t T_UK = 0;      // 2 x 128
 constexpr uint32_t T_KV = 256;    // 2 x 128 (80 used): [KV (64) | sum phi(K) (16 identical columns)] for feature blocks 0-127, 128-255
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   uint64_t* a_full = bars + 16;   // [2] phi(K) tile written to shared memory
   uint64_t* a_free = bars + 18;   // [2] phi(K) tile consumed (MMAs done + bulk store has read it)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
-  float* red = reinterpret_cast<float*>(bars + 24);  // [8]
+  float* red = reinterpret_cast<float*>(bars + 24);  // [NFEAT / 32]
   constexpr int KD = MAX_ONLY ? 4 : 2;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -269,7 +272,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     }
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == WPK) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -289,7 +292,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     return row0 >= a.sum_lo && row0 + TILE <= a.sum_hi && a.k_pos0 + row0 + TILE <= len_b;
   };
 
-  if (warp == 8) {
+  if (warp == WPK) {
     // ---------------- producer ----------------
     const bool leader = elect_one();
     if (leader) {
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
+  } else if (warp == WPK + 1) {
     // ---------------- MMA issuer ----------------
     const bool leader = elect_one();
     constexpr uint32_t id_uk = idesc_bf16(128, 128, false, false);
@@ -389,7 +392,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     __syncwarp();
   } else {
     // ---------------- feature warps ----------------
-    const int qd = warp & 3, hf = warp >> 2;
+    const int qd = warp & 3, cq = warp >> 2;
+    constexpr int PWK = 128 / NFQ;                   // projections owned by this thread
     const int krow = qd * 32 + lane;                 // key row inside the tile
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
     const float beta = MAX_ONLY ? 0.f : a.beta_in[bh];
@@ -406,9 +410,9 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       if (MAX_ONLY) {
         float mx = 0.f;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < CHK; ++c) {
           uint32_t r[32];
-          tmem_ld32(lane_base + T_UK + s * 128 + 64 * hf + 32 * c, r);
+          tmem_ld32(lane_base + T_UK + s * 128 + PWK * cq + 32 * c, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fabsf(__uint_as_float(r[j])));
@@ -424,8 +428,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         __nv_bfloat16* grow = a.phik + ((int64_t)bh * a.S + row) * kM;
         uint8_t* sA = smem + OFF_A + s * 65536;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int f0 = 64 * hf + 32 * c;           // first projection of this chunk
+        for (int c = 0; c < CHK; ++c) {
+          const int f0 = PWK * cq + 32 * c;          // first projection of this chunk
           uint32_t r[32];
           tmem_ld32(lane_base + T_UK + s * 128 + f0, r);
           tmem_ld_wait();
@@ -448,7 +452,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
           if (c == 0 && i >= 2) mbar_wait(a_free + s, ((i >> 1) - 1) & 1, a.status, 17);
           if (c == 0 && i < 9) TRACE(2 + 3 * i);
           // MN-major A operand: block = feature / 64, 16-byte chunk = (feature % 64) / 8, swizzled by key % 8
-          const int blk = f0 >> 6;                   // = hf
+          const int blk = f0 >> 6;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int chunk = ((f0 & 63) >> 3) + q;
@@ -471,41 +475,47 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) run_max = fmaxf(run_max, __shfl_xor_sync(0xffffffffu, run_max, o));
       if (lane == 0) red[warp] = run_max;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(NFEAT) : "memory");
       if (tid == 0) {
         float v = red[0];
-        for (int i = 1; i < 8; ++i) v = fmaxf(v, red[i]);
+        for (int i = 1; i < NFEAT / 32; ++i) v = fmaxf(v, red[i]);
         if (v > -INFINITY) atomic_max_float(a.beta_out + bh, v);
       }
     } else {
       mbar_wait(bar_done, 0, a.status, 18);
       tc_fence_after_sync();
       TRACE(30);
-      // thread (feature row, half): half 0 writes KV columns 0-31, half 1 columns 32-63 and the feature sum
+      // thread (feature row, group): writes 64/NFQ of the row's KV columns; the last group also the feature sum
+      constexpr int CW = 64 / NFQ;
       float* part = a.partial + ((int64_t)bh * a.nsplit + split) * kM * kPartialLd;
 #pragma unroll
       for (int mb = 0; mb < 2; ++mb) {
         float* prow = part + (int64_t)(mb * 128 + krow) * kPartialLd;
-        uint32_t r[32], q[16];
-        tmem_ld32(lane_base + T_KV + mb * 128 + 32 * hf, r);
+        uint32_t q[16];
         tmem_ld16(lane_base + T_KV + mb * 128 + 64, q);
-        tmem_ld_wait();
-        if (nt == 0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
-          q[0] = 0u;
+        for (int gq = 0; gq < CW / 16; ++gq) {
+          uint32_t r[16];
+          tmem_ld16(lane_base + T_KV + mb * 128 + CW * cq + 16 * gq, r);
+          tmem_ld_wait();
+          if (nt == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<uint4*>(prow + CW * cq + 16 * gq)[j] =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          reinterpret_cast<uint4*>(prow + 32 * hf)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        if (hf == 1) prow[64] = __uint_as_float(q[0]);
+        tmem_ld_wait();
+        if (cq == NFQ - 1) prow[64] = nt == 0 ? 0.f : __uint_as_float(q[0]);
       }
     }
   }
   if (!MAX_ONLY && tid == 0) TRACE(31);
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == WPK) {
     __syncwarp();
     tmem_dealloc(tb, 512);
   }
@@ -1082,18 +1092,19 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + T.b * p.o_stride_b + T.h * p.o_stride_h +
                             (int64_t)(T.i0 + row) * p.o_stride_t + OW * cq;
-      {
+#pragma unroll
+      for (int og = 0; og < OW / 16; ++og) {
         // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
         uint32_t ro[16];
-        tmem_ld16(lane_base + T_O + OW * cq, ro);
+        tmem_ld16(lane_base + T_O + OW * cq + 16 * og, ro);
         tmem_ld_wait();
         uint32_t o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
         if (row < T.nq) {
-          reinterpret_cast<uint4*>(orow)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          reinterpret_cast<uint4*>(orow)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          reinterpret_cast<uint4*>(orow + 16 * og)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          reinterpret_cast<uint4*>(orow + 16 * og)[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
       TRACEB(21);
