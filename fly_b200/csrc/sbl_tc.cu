@@ -166,19 +166,6 @@ __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64
 }
 
 // ---------------------------------------------------------------------------
-#ifdef SBL_TRACE
-__device__ long long g_trace[64][32];
-__device__ long long g_trace2[64][2][32];   // [cta][0 = producer, 1 = MMA issuer][slot]
-#define TRACE(slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (threadIdx.x == 0)) g_trace[blockIdx.y * 8 + blockIdx.x][slot] = clock64(); } while (0)
-#define TRACEC(cond, slot) do { if ((cond) && blockIdx.x < 64) g_trace[blockIdx.x][slot] = clock64(); } while (0)
-#define TRACEB(slot) do { if (it == 2 && blockIdx.x < 64 && threadIdx.x == 0) g_trace[blockIdx.x][slot] = clock64(); } while (0)
-#define TRACE2(who, slot) do { if (blockIdx.x < 8 && blockIdx.y < 8 && (slot) < 32) g_trace2[blockIdx.y * 8 + blockIdx.x][who][slot] = clock64(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#define TRACEB(slot) do { } while (0)
-#define TRACEC(cond, slot) do { } while (0)
-#define TRACE2(who, slot) do { } while (0)
-#endif
 
 // keys kernel
 struct KeysArgs {
@@ -251,7 +238,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
   const int t_hi = (int)((int64_t)ntiles * (split + 1) / a.nsplit);
   const int nt = t_hi - t_lo;
   const int64_t len_b = a.lengths ? min(a.lengths[b], a.S_total) : a.S_total;
-  if (!MAX_ONLY && tid == 0) TRACE(0);
 
   if (tid == 0) {
     mbar_init(bar_w, 1);
@@ -338,7 +324,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       mbar_wait(v_full + s, (u >> 1) & 1, a.status, 14);
       tc_fence_after_sync();
       if (leader) {
-        if (!MAX_ONLY) TRACE2(1, 2 * u);
         // bulk copy of the phi(K) tile to the workspace (an empty group keeps the group count uniform)
         if (tile_is_plain(u)) {
           const int row0 = (t_lo + u) * TILE;
@@ -362,7 +347,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
           tma_store_wait_read1();
           mbar_arrive(a_free + (s ^ 1));
         }
-        if (!MAX_ONLY) TRACE2(1, 2 * u + 1);
       }
       __syncwarp();
     };
@@ -406,7 +390,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       mbar_wait(uk_full + s, (i >> 1) & 1, a.status, 16);   // U computed: the tensor core is done with the K tile too
       tc_fence_after_sync();
       mbar_arrive(k_free + (i % KD));
-      if (!MAX_ONLY && i < 9) TRACE(1 + 3 * i);
       if (MAX_ONLY) {
         float mx = 0.f;
 #pragma unroll
@@ -450,7 +433,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
           }
           // the previous tile's MMAs and bulk store must be done with the shared phi(K) buffer
           if (c == 0 && i >= 2) mbar_wait(a_free + s, ((i >> 1) - 1) & 1, a.status, 17);
-          if (c == 0 && i < 9) TRACE(2 + 3 * i);
           // MN-major A operand: block = feature / 64, 16-byte chunk = (feature % 64) / 8, swizzled by key % 8
           const int blk = f0 >> 6;
 #pragma unroll
@@ -468,7 +450,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         tc_fence_before_sync();
         mbar_arrive(a_full + s);
         mbar_arrive(uk_free + s);
-        if (i < 9) TRACE(3 + 3 * i);
       }
     }
     if (MAX_ONLY) {
@@ -484,7 +465,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     } else {
       mbar_wait(bar_done, 0, a.status, 18);
       tc_fence_after_sync();
-      TRACE(30);
       // thread (feature row, group): writes 64/NFQ of the row's KV columns; the last group also the feature sum
       constexpr int CW = 64 / NFQ;
       float* part = a.partial + ((int64_t)bh * a.nsplit + split) * kM * kPartialLd;
@@ -512,7 +492,6 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       }
     }
   }
-  if (!MAX_ONLY && tid == 0) TRACE(31);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == WPK) {
@@ -677,16 +656,13 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     auto load_qw = [&](int it2) {
       if (it2 >= n_it) return;
       const BandTile T2 = band_tile(a, tile_lo + it2);
-      if (leader) TRACEC(it2 == 2, 22);
       if (it2 >= 1) mbar_wait(bars + B_QFREE, (it2 - 1) & 1, a.status, 20);
       if (leader) {
-        TRACEC(it2 == 2, 23);
         mbar_expect_tx(bars + B_Q, 16384);
         tma_load_4d(smem + OFF_Q, &a.tm_q, bars + B_Q, 0, T2.i0, T2.h, T2.b);
       }
       if (it2 >= 1) mbar_wait(bars + B_WFREE, (it2 - 1) & 1, a.status, 21);
       if (leader) {
-        TRACEC(it2 == 2, 24);
         mbar_expect_tx(bars + B_W, 16384);
         tma_load_2d(smem + OFF_KV, &a.tm_w, bars + B_W, 0, 0);
       }
@@ -793,15 +769,11 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       const BandTile T = band_tile(a, tile_lo + it);
       const int nt = T.nt;
       // U = Q Wt^T into the buffer of key tile gk+1; that buffer last held key tile gk-1
-      if (leader) TRACEC(it == 2, 25);
       mbar_wait(bars + B_Q, it & 1, a.status, 30);
-      if (leader) TRACEC(it == 2, 26);
       mbar_wait(bars + B_W, it & 1, a.status, 30);
-      if (leader) TRACEC(it == 2, 27);
       if (gk >= 1) b_done_wait(gk - 1);
       tc_fence_after_sync();
       if (leader) {
-        TRACEC(it == 2, 28);
         const uint32_t td = tb + T_BUF + ((gk + 1) & 1) * 128;
         mma_ss(td, dQ, dKV, id_n128, false);
         mma_ss(td, dQ + 2, dKV + 2, id_n128, true);
@@ -892,21 +864,17 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       const int nt = T.nt;
       const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
       const int gi_first = (int)p.q_pos0 + T.i0 + qd * 32, gi_last = gi_first + 31;   // rows of this warp
-      TRACEB(0);
       // s_ksum / s_xch are free again: every thread passed the exchange of the previous tile
       for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)T.bh * kM + i];
       asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
       // ---- phi(Q): this thread's PW projections -> 2*PW features ----
-      TRACEB(1);
       mbar_wait(bars + B_Q, it & 1, a.status, 33);
-      TRACEB(2);
       const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
       mbar_arrive(bars + B_QFREE);
       const float g = 0.5f * p.softmax_temp * qn2;
       const float M = sqrtf(qn2) * wmax;             // >= |u_f| for every feature (Cauchy-Schwarz)
       mbar_wait(bars + B_UQ, it & 1, a.status, 34);
       tc_fence_after_sync();
-      TRACEB(3);
       float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
       {
         const float mo = -M * kLog2e;
@@ -936,7 +904,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       }
       tc_fence_before_sync();
       mbar_arrive(bars + B_PHIQ);
-      TRACEB(4);
 
       const float pls = (-g + M - half_log_m) + a.beta[T.bh];       // query log-scale + key log-scale
       const float co = -pls * kLog2e;                               // exp(tau s - pls) = ex2(s * sc + co)
@@ -960,7 +927,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           const int whi_min = col_hi(u, gi_first), whi = col_hi(u, gi_last);
           mbar_wait(bars + B_SFULL + s, (gg >> 1) & 1, a.status, 35);
           tc_fence_after_sync();
-          if (u < 3) TRACEB(5 + 4 * u);
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
             const int c0 = PW * cq + 32 * c;
@@ -1004,7 +970,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           }
           tc_fence_before_sync();
           mbar_arrive(bars + B_ADONE + s);
-          if (u < 3) TRACEB(6 + 4 * u);
         }
         if (t >= 0) {
           // B: P(t) -> D = E - P (packed bf16 into tensor memory), row sum dps
@@ -1015,7 +980,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           mbar_wait(bars + B_PFULL + s, (gg >> 1) & 1, a.status, 36);
           if (gg >= 1) mbar_wait(bars + B_DFREE, (gg - 1) & 1, a.status, 37);
           tc_fence_after_sync();
-          if (t < 3) TRACEB(7 + 4 * t);
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
             const int c0 = PW * cq + 32 * c;
@@ -1064,7 +1028,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           tmem_st_wait();
           tc_fence_before_sync();
           mbar_arrive(bars + B_BDONE + s);
-          if (t < 3) TRACEB(8 + 4 * t);
         }
 #pragma unroll
         for (int j = 0; j < 16 * CH; ++j) Ec[j] = En[j];
@@ -1085,10 +1048,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         Z += s_xch[2 * NSOFT + m8];
       }
       // ---- epilogue: this thread writes 64/NCQ of the row's 64 outputs ----
-      TRACEB(19);
       mbar_wait(bars + B_DONE, it & 1, a.status, 38);
       tc_fence_after_sync();
-      TRACEB(20);
       const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + T.b * p.o_stride_b + T.h * p.o_stride_h +
                             (int64_t)(T.i0 + row) * p.o_stride_t + OW * cq;
@@ -1107,7 +1068,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           reinterpret_cast<uint4*>(orow + 16 * og)[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
-      TRACEB(21);
       // O has been read: the next query tile's phi(Q) arrival (B_PHIQ) releases the low-rank MMA that overwrites it
       gk += nt;
     }
@@ -1307,15 +1267,6 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   tc_band_kernel<<<grid, band::NTHREADS, band::SMEM_BYTES, st>>>(a);
   return cudaGetLastError();
 }
-
-#ifdef SBL_TRACE
-extern "C" int sbl_trace_fetch(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * 64 * 32);
-}
-extern "C" int sbl_trace_fetch2(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace2, sizeof(long long) * 64 * 2 * 32);
-}
-#endif
 
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st) {
   cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, sizeof(int), cudaMemcpyDeviceToHost, st);
