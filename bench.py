@@ -273,25 +273,54 @@ def main():
     layer = SBLocalAttention(w, d, m).to(dev).eval()
     layer.feature_map.new_feature_map(dev)
     layer.feature_map.projection_matrix.copy_(Wd)
-    out_h = torch.empty(B, N, H, d, dtype=q_h.dtype).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
+    # Three streams, two buffer sets: the host->device copy of step i+1 and the device->host copy of
+    # step i-1 overlap the kernels of step i (PCIe is full duplex).  Every step still copies its own
+    # q, k, v from pinned host memory and its own output back to pinned host memory.
+    s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dev_in = [[torch.empty_like(x, device=dev) for x in (q_h, k_h, v_h)] for _ in range(2)]
+    out_hs = [torch.empty(B, N, H, d, dtype=q_h.dtype).pin_memory() for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_cmp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step():
-        qd, kd, vd = q_h.to(dev, non_blocking=True), k_h.to(dev, non_blocking=True), v_h.to(dev, non_blocking=True)
-        with torch.no_grad():
-            o, _ = layer(qd, kd, vd)
-        out_h.copy_(o, non_blocking=True)
+    def e2e_run(n):
+        for i in range(n):
+            bset = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_cmp[bset])        # kernels of step i-2 are done with this input set
+                for dst, src in zip(dev_in[bset], (q_h, k_h, v_h)):
+                    dst.copy_(src, non_blocking=True)
+                ev_in[bset].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[bset])
+                with torch.no_grad():
+                    o, _ = layer(*dev_in[bset])
+                ev_cmp[bset].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[bset])
+                if i >= 2:
+                    s_out.wait_event(ev_out[bset])       # (same stream, kept for clarity) host buffer reuse
+                o.record_stream(s_out)
+                out_hs[bset].copy_(o, non_blocking=True)
+                ev_out[bset].record(s_out)
+        for st_ in (s_in, s_cmp, s_out):
+            torch.cuda.current_stream(dev).wait_stream(st_)
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    s1.record()
-    barrier()
-    e2e_ms = s0.elapsed_time(s1)
+    e2e_run(3)
+    e2e_reps = []
+    for _ in range(3):                                   # host-link bandwidth is noisy: median of 3 repeats
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for st_ in (s_in, s_cmp, s_out):
+            st_.wait_stream(torch.cuda.current_stream(dev))
+        e2e_run(e2e_steps)
+        s1.record()
+        barrier()
+        e2e_reps.append(s0.elapsed_time(s1))
+    e2e_ms = sorted(e2e_reps)[1]
 
     t = torch.tensor([ms, e2e_ms, band_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -328,7 +357,8 @@ def main():
                         kernels='tcgen05+TMA bf16' if tensor_path else 'generic SIMT fp32 math'),
             clocks=clocks,
             e2e=dict(value=e2e_value, unit='tokens/s', h2d_bytes_per_step=3 * th * d * elem,
-                     d2h_bytes_per_step=th * d * elem, steps=e2e_steps),
+                     d2h_bytes_per_step=th * d * elem, steps=e2e_steps,
+                     pipeline='3 streams, 2 buffer sets: copies of neighbouring steps overlap the kernels'),
             gpu_launches=launches_per_step * args.steps,
             roofline=dict(bound='tensor', kernel='band', achieved=achieved, peak=peak_tf, unit='TFLOP/s',
                           frac=achieved / peak_tf, traffic=band_traffic, peak_source=peaks['source'],
