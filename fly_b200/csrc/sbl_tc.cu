@@ -49,6 +49,51 @@ __device__ __forceinline__ void atomic_max_float(float* addr, float v) {
   else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
 }
 
+// Packed fp32 pairs (one issue slot for two lanes of arithmetic).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// v if bit k of mask is set, else 0 (two instructions: shift the bit into the sign, select on the sign)
+__device__ __forceinline__ float keep_if_bit(float v, uint32_t mask, int k) {
+  float d;
+  asm("slct.f32.s32 %0, %1, %2, %3;" : "=f"(d) : "f"(0.f), "f"(v), "r"((int)(mask << (31 - k))));
+  return d;
+}
+
+// sum of squares of elements 16*part .. 16*part+15 of one 64-element bf16 row held in a 128-byte swizzled line
+__device__ __forceinline__ float quarter_row_sumsq_sw128(const uint8_t* tile, int row, int part) {
+  float2 s = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const uint4 v = *reinterpret_cast<const uint4*>(tile + row * 128 + (((2 * part + c) ^ (row & 7)) << 4));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = make_float2(bf16_lo(w[j]), bf16_hi(w[j]));
+      s = fma2(x, x, s);
+    }
+  }
+  return s.x + s.y;
+}
+
 // sum of squares of one 64-element bf16 row held in a 128-byte swizzled line
 __device__ __forceinline__ float row_sumsq_sw128(const uint8_t* tile, int row) {
   float s = 0.f;
@@ -502,6 +547,20 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
 
 // ---------------------------------------------------------------------------
 // band kernel
+// Debug builds (-DSBL_TRACE) record clock64() at the phase boundaries of one query tile per CTA; the
+// regular build compiles the marks away.
+#ifdef SBL_TRACE
+__device__ long long g_band_trace[160][96];
+#define SBL_MARK(cond, slot)                                   \
+  do {                                                         \
+    if (cond) g_band_trace[blockIdx.x][slot] = clock64();      \
+  } while (0)
+constexpr int kTraceIt = 5;
+#else
+#define SBL_MARK(cond, slot) \
+  do {                       \
+  } while (0)
+#endif
 struct BandArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_w, tm_phik, tm_kv;
   SblParams p;
@@ -517,7 +576,6 @@ namespace band {
 constexpr int BQ = 128, KT = 128;
 constexpr int NCQ = 4;                     // column groups per row: a softmax thread owns 128/NCQ key columns of a tile
 constexpr int NSOFT = 128 * NCQ;           // softmax threads: warp w owns rows 32*(w%4).., column group w/4
-constexpr int CH = 4 / NCQ;                // 32-column chunks per thread and tile
 constexpr int WP = NSOFT / 32;             // first non-softmax warp: producer; WP+1: MMA (U, S, O, low-rank); WP+2: MMA (P)
 constexpr int NTHREADS = NSOFT + 96;
 constexpr uint32_t OFF_Q = 0;              // 16 KB [128 q][64 e]
@@ -525,7 +583,7 @@ constexpr uint32_t OFF_KV = 16384;         // 32 KB [256 f][64 d]; its first 16 
 constexpr uint32_t OFF_K = 49152;          // 16 KB [128 keys][64 e]
 constexpr uint32_t OFF_V = OFF_K + 16384;  // 16 KB [128 keys][64 d]
 constexpr uint32_t OFF_PK = OFF_V + 16384; // 2 x 64 KB: phi(K) tiles, each 4 blocks [128 keys][64 f]
-constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + exchange fp32[3][NSOFT]
+constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + |q|^2 partials fp32[NSOFT] + exchange fp32[2][NSOFT]
 constexpr uint32_t OFF_BAR = OFF_MISC + 1024 + 12 * NSOFT;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;
 // tensor memory columns
@@ -550,7 +608,8 @@ enum {
   B_ADONE = B_SFULL + 2,                             // [2] NSOFT arrivals
   B_PFULL = B_ADONE + 2,                             // [2]
   B_BDONE = B_PFULL + 2,                             // [2] NSOFT arrivals
-  B_COUNT = B_BDONE + 2
+  B_SISS = B_BDONE + 2,                              // S of a third or later key tile has been issued (orders P behind it)
+  B_COUNT
 };
 static_assert(B_COUNT <= 32, "one barrier per lane of the initialising warp");
 }  // namespace band
@@ -559,13 +618,24 @@ static_assert(B_COUNT <= 32, "one barrier per lane of the initialising warp");
 struct BandTile {
   int bh, b, h, i0, nq, len_b, j0, nt;
 };
-__device__ __forceinline__ BandTile band_tile(const BandArgs& a, int tile_id) {
+// A CTA walks consecutive tiles: (b*h, query tile) advance without dividing by the tile count.
+struct TileCursor {
+  int bh, qt;
+  __device__ TileCursor(const BandArgs& a, int tile_id) : bh(tile_id / a.ntq), qt(tile_id % a.ntq) {}
+  __device__ void next(const BandArgs& a) {
+    if (++qt == a.ntq) {
+      qt = 0;
+      ++bh;
+    }
+  }
+};
+__device__ __forceinline__ BandTile band_tile(const BandArgs& a, const TileCursor& c) {
   const SblParams& p = a.p;
   BandTile t;
-  t.bh = tile_id / a.ntq;
+  t.bh = c.bh;
   t.b = t.bh / p.H;
-  t.h = t.bh % p.H;
-  t.i0 = (tile_id % a.ntq) * band::BQ;
+  t.h = t.bh - t.b * p.H;
+  t.i0 = c.qt * band::BQ;
   t.nq = min(band::BQ, p.T - t.i0);
   t.len_b = (int)(p.key_lengths ? min(p.key_lengths[t.b], p.S_total) : p.S_total);
   const int hw = p.w / 2;
@@ -610,7 +680,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);
-  float* s_xch = s_ksum + kM;       // [3][NSOFT]
+  float* s_sq = s_ksum + kM;        // [NSOFT]
+  float* s_xch = s_sq + NSOFT;      // [2][NSOFT]
 
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -653,9 +724,11 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     PkTrack pk;
     // Q and Wt of query tile `it2`: issued as soon as the previous tile has released the two buffers,
     // i.e. in the middle of the previous tile, so that U = Q Wt^T of the next tile is ready at its start
-    auto load_qw = [&](int it2) {
+    TileCursor cur(a, tile_lo), cur_next(a, tile_lo);
+    auto load_qw = [&](int it2) {   // called once per it2, in order: cur_next is the cursor of tile it2
       if (it2 >= n_it) return;
-      const BandTile T2 = band_tile(a, tile_lo + it2);
+      const BandTile T2 = band_tile(a, cur_next);
+      cur_next.next(a);
       if (it2 >= 1) mbar_wait(bars + B_QFREE, (it2 - 1) & 1, a.status, 20);
       if (leader) {
         mbar_expect_tx(bars + B_Q, 16384);
@@ -668,8 +741,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       }
     };
     load_qw(0);
-    for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, tile_lo + it);
+    for (int it = 0; it < n_it; ++it, cur.next(a)) {
+      const BandTile T = band_tile(a, cur);
       // K and V are single-buffered, phi(K) double-buffered.  Issue order follows the order
       // in which the tensor core frees the buffers: K(g), phi(K)(g), then V(g-1).
       auto load_v = [&](int t) {
@@ -688,8 +761,11 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           tma_load_3d(smem + OFF_KV, &a.tm_kv, bars + B_KV, 0, 0, T.bh);
         }
       };
+      // The last key tile of a query tile is the one no earlier tile of the run has touched, and its V is
+      // loaded last, behind a single buffer: start pulling it into L2 now.
+      if (leader && T.nt >= 2) tma_prefetch_4d(&a.tm_v, 0, T.j0 + (T.nt - 1) * KT, T.h, T.b);
       for (int t = 0; t < T.nt; ++t) {
-        const int g = gk + t, s = g & 1, row0 = T.j0 + t * KT;
+        const int g = gk + t, row0 = T.j0 + t * KT;
         if (g >= 1) mbar_wait(bars + B_KEMPTY, (g - 1) & 1, a.status, 21);
         if (leader) {
           mbar_expect_tx(bars + B_KFULL, 16384);
@@ -737,7 +813,9 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     auto b_done_wait = [&](int g) {   // B of key tile g finished: its buffer and D are consumed
       mbar_wait(bars + B_BDONE + (g & 1), (g >> 1) & 1, a.status, 28);
     };
-    auto issue_s = [&](int g, bool last) {
+    // tell_b: issuer B holds P of the previous key tile back until this S is in the queue, so that the
+    // softmax warps get their next S before the (four times longer) P
+    auto issue_s = [&](int g, bool last, bool tell_b) {
       mbar_wait(bars + B_KFULL, g & 1, a.status, 25);
       tc_fence_after_sync();
       if (leader) {
@@ -749,6 +827,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         mma_commit(bars + B_KEMPTY);
         mma_commit(bars + B_SFULL + (g & 1));
         if (last) mma_commit(bars + B_QFREE);   // no later MMA of this query tile reads Q
+        if (tell_b) mbar_arrive(bars + B_SISS);
       }
       __syncwarp();
     };
@@ -765,8 +844,9 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       }
       __syncwarp();
     };
-    for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, tile_lo + it);
+    TileCursor cur(a, tile_lo);
+    for (int it = 0; it < n_it; ++it, cur.next(a)) {
+      const BandTile T = band_tile(a, cur);
       const int nt = T.nt;
       // U = Q Wt^T into the buffer of key tile gk+1; that buffer last held key tile gk-1
       mbar_wait(bars + B_Q, it & 1, a.status, 30);
@@ -781,16 +861,20 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         mma_ss(td, dQ + 6, dKV + 6, id_n128, true);
         mma_commit(bars + B_UQ);
         if (nt == 0) mma_commit(bars + B_QFREE);
+        SBL_MARK(it == kTraceIt, 20);
       }
       __syncwarp();
       // S(0) does not need phi(Q): it runs while the softmax warps form it (its buffer last held key tile gk-2)
       if (nt > 0) {
         if (gk >= 2) b_done_wait(gk - 2);
-        issue_s(gk, nt == 1);
+        issue_s(gk, nt == 1, false);
+        SBL_MARK(leader && it == kTraceIt, 21);
       }
       mbar_wait(bars + B_PHIQ, it & 1, a.status, 31);
       tc_fence_after_sync();
-      if (nt > 1) issue_s(gk + 1, nt == 2);
+      SBL_MARK(leader && it == kTraceIt, 22);
+      if (nt > 1) issue_s(gk + 1, nt == 2, false);
+      SBL_MARK(leader && it == kTraceIt, 23);
       // O starts as the low-rank numerator phi(Q) KV; the band tiles accumulate onto it
       mbar_wait(bars + B_KV, it & 1, a.status, 32);
       tc_fence_after_sync();
@@ -799,50 +883,64 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         for (int k = 0; k < 16; ++k)
           mma_ts(tb + T_O, tb + T_PHIQ + k * 8, dKV + (uint64_t)(k * (2048 >> 4)), id_o, k > 0);
         mma_commit(bars + B_WFREE);
+        SBL_MARK(it == kTraceIt, 24);
       }
       __syncwarp();
       for (int t = 1; t < nt; ++t) {
         // both need B(t-1) finished; S first, the softmax warps are waiting for it
         if (t + 1 < nt) {
           b_done_wait(gk + t - 1);
-          issue_s(gk + t + 1, t + 2 == nt);
+          issue_s(gk + t + 1, t + 2 == nt, true);
+          SBL_MARK(leader && it == kTraceIt, 25);
         }
         issue_o(gk + t - 1);
+        SBL_MARK(leader && it == kTraceIt && t < 3, 25 + t);
       }
       if (nt > 0) issue_o(gk + nt - 1);
+      SBL_MARK(leader && it == kTraceIt, 28);
       if (leader) mma_commit(bars + B_DONE);
       __syncwarp();
       gk += nt;
     }
   } else if (warp == WP + 2) {
-    // ---------------- MMA issuer B: P(g) = phi(Q) phi(K)^T over the buffer that held S(g) ----------------
+    // ---------------- MMA issuer B: buffer(g) -= phi(Q) phi(K)^T ----------------
+    // The buffer holds E = exp(tau S - pls) written back by the softmax warps; the product is accumulated
+    // with the A operand negated, which leaves D = E - P in fp32.
     // (its own warp, on another scheduler than issuer A: the two issue streams run in parallel)
     const bool leader = elect_one();
-    constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
+    constexpr uint32_t id_neg = idesc_bf16(128, 128, false, false) | (1u << 13);   // bit 13: negate A
     const uint64_t dPK0 = smem_desc_sw128(smem_u32(smem + OFF_PK), 16, 1024);
     int gk = 0;
     PkTrack pk;
-    for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, tile_lo + it);
+    TileCursor cur(a, tile_lo);
+    int nsiss = 0;
+    for (int it = 0; it < n_it; ++it, cur.next(a)) {
+      const BandTile T = band_tile(a, cur);
       mbar_wait(bars + B_PHIQ, it & 1, a.status, 39);
       for (int t = 0; t < T.nt; ++t) {
         const int g = gk + t, s = g & 1;
         const int kt = T.j0 / KT + t, ps = kt & 1;
         mbar_wait(bars + B_ADONE + s, (g >> 1) & 1, a.status, 26);
+        SBL_MARK(leader && it == kTraceIt && t < 3, 34 + t);
         if (!pk.resident(ps, T.bh, kt)) {   // a tile still resident from the previous query tile was waited for then
           mbar_wait(bars + B_PKFULL + ps, pk.fills(ps) & 1, a.status, 27);
           pk.filled(ps, T.bh, kt);
         }
         pk.used(ps);
+        if (t >= 1 && t + 1 < T.nt) {   // S(t+1) goes first
+          mbar_wait(bars + B_SISS, nsiss & 1, a.status, 41);
+          ++nsiss;
+        }
         tc_fence_after_sync();
         if (leader) {
           const uint64_t dPK = dPK0 + (uint64_t)(ps * (65536 >> 4));
           const uint32_t td = tb + T_BUF + s * 128;
 #pragma unroll
           for (int k = 0; k < 16; ++k)
-            mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_n128, k > 0);
+            mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_neg, true);
           mma_commit(bars + B_PKEMPTY + ps);
           mma_commit(bars + B_PFULL + s);
+          SBL_MARK(it == kTraceIt && t < 3, 30 + t);
         }
         __syncwarp();
       }
@@ -850,52 +948,69 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     }
   } else {
     // ---------------- softmax warps ----------------
+    static_assert(NCQ == 4, "a softmax thread owns one 32-column chunk of a key tile and 16 output columns");
     const int qd = warp & 3, cq = warp >> 2;         // lane quarter (rows), column group
     const int row = qd * 32 + lane;                  // query row of this thread
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
     constexpr int PW = 128 / NCQ;                    // projections (and key columns per tile) owned by this thread
     constexpr int OW = 64 / NCQ;                     // output columns owned by this thread
+    const int c0 = PW * cq;                          // first key column (of every key tile) of this thread
     const float wmax = __ldg(a.wmax);
     const float half_log_m = 0.5f * logf((float)kM);
     const float sc = p.softmax_temp * kLog2e;
-    int gk = 0;
-    for (int it = 0; it < n_it; ++it) {
-      const BandTile T = band_tile(a, tile_lo + it);
+    int gk = 0, bh_smem = -1;
+    TileCursor cur(a, tile_lo);
+    for (int it = 0; it < n_it; ++it, cur.next(a)) {
+      const BandTile T = band_tile(a, cur);
       const int nt = T.nt;
       const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
-      const int gi_first = (int)p.q_pos0 + T.i0 + qd * 32, gi_last = gi_first + 31;   // rows of this warp
-      // s_ksum / s_xch are free again: every thread passed the exchange of the previous tile
-      for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)T.bh * kM + i];
-      asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
-      // ---- phi(Q): this thread's PW projections -> 2*PW features ----
+      const float beta = __ldg(a.beta + T.bh);       // needed after phi(Q): the load has a whole phase to land
+#ifdef SBL_TRACE
+      const bool tr = it == kTraceIt && lane == 0 && (warp == 0 || warp == 15);
+      const int trb = warp == 0 ? 0 : 48;
+#endif
+      SBL_MARK(tr, trb + 0);
+      // s_ksum is free again: every thread passed the exchange of the previous tile
+      if (T.bh != bh_smem) {
+        for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)T.bh * kM + i];
+        bh_smem = T.bh;
+      }
+      // ---- |q|^2: the four threads of a row each sum 16 of its 64 elements ----
       mbar_wait(bars + B_Q, it & 1, a.status, 33);
-      const float qn2 = row_sumsq_sw128(smem + OFF_Q, row);
+      SBL_MARK(tr, trb + 1);
+      s_sq[tid] = quarter_row_sumsq_sw128(smem + OFF_Q, row, cq);
       mbar_arrive(bars + B_QFREE);
+      asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
+      const float qn2 = (s_sq[row] + s_sq[128 + row]) + (s_sq[256 + row] + s_sq[384 + row]);
       const float g = 0.5f * p.softmax_temp * qn2;
       const float M = sqrtf(qn2) * wmax;             // >= |u_f| for every feature (Cauchy-Schwarz)
+      SBL_MARK(tr, trb + 2);
+      // ---- phi(Q): this thread's PW projections -> 2*PW features ----
       mbar_wait(bars + B_UQ, it & 1, a.status, 34);
       tc_fence_after_sync();
-      float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
+      SBL_MARK(tr, trb + 3);
+      float2 zp = make_float2(0.f, 0.f), zm = make_float2(0.f, 0.f);
       {
         const float mo = -M * kLog2e;
+        const float2 mo2 = make_float2(mo, mo);
+        const float2 lp = make_float2(kLog2e, kLog2e), lm = make_float2(-kLog2e, -kLog2e);
         const uint32_t t_uq = lane_base + T_BUF + ((gk + 1) & 1) * 128;
 #pragma unroll
-        for (int c = 0; c < 2 * CH; ++c) {
-          const int f0 = PW * cq + 16 * c;           // first projection index of this group of 16
+        for (int c = 0; c < 2; ++c) {
+          const int f0 = c0 + 16 * c;                // first projection index of this group of 16
           uint32_t r[16];
           tmem_ld16(t_uq + f0, r);
           tmem_ld_wait();
           uint32_t p1[8], p2[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float u0 = __uint_as_float(r[2 * j]) * kLog2e, u1 = __uint_as_float(r[2 * j + 1]) * kLog2e;
-            p1[j] = pack_bf16(ex2(u0 + mo), ex2(u1 + mo));
-            p2[j] = pack_bf16(ex2(mo - u0), ex2(mo - u1));
-            // Z from the rounded features, so that Z - dps cancels what the MMA sees
-            z0 = fmaf(bf16_lo(p1[j]), s_ksum[f0 + 2 * j], z0);
-            z1 = fmaf(bf16_hi(p1[j]), s_ksum[f0 + 2 * j + 1], z1);
-            z2 = fmaf(bf16_lo(p2[j]), s_ksum[kR + f0 + 2 * j], z2);
-            z3 = fmaf(bf16_hi(p2[j]), s_ksum[kR + f0 + 2 * j + 1], z3);
+            const float2 u = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            const float2 ap = fma2(u, lp, mo2), am = fma2(u, lm, mo2);
+            const float2 ep = make_float2(ex2(ap.x), ex2(ap.y)), em = make_float2(ex2(am.x), ex2(am.y));
+            p1[j] = pack_bf16(ep.x, ep.y);
+            p2[j] = pack_bf16(em.x, em.y);
+            zp = fma2(ep, *reinterpret_cast<const float2*>(s_ksum + f0 + 2 * j), zp);
+            zm = fma2(em, *reinterpret_cast<const float2*>(s_ksum + kR + f0 + 2 * j), zm);
           }
           tmem_st8(lane_base + T_PHIQ + f0 / 2, p1);
           tmem_st8(lane_base + T_PHIQ + 64 + f0 / 2, p2);
@@ -904,171 +1019,154 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       }
       tc_fence_before_sync();
       mbar_arrive(bars + B_PHIQ);
+      SBL_MARK(tr, trb + 4);
 
-      const float pls = (-g + M - half_log_m) + a.beta[T.bh];       // query log-scale + key log-scale
-      const float co = -pls * kLog2e;                               // exp(tau s - pls) = ex2(s * sc + co)
-      float L = 0.f, dps = 0.f;
-      uint32_t Ec[16 * CH], En[16 * CH];   // exp(tau S - pls), packed bf16: tile being finished / tile just started
+      const float pls = (-g + M - half_log_m) + beta;               // query log-scale + key log-scale
+      const float2 sc2 = make_float2(sc, sc);
+      const float2 co2 = make_float2(-pls * kLog2e, -pls * kLog2e);  // exp(tau s - pls) = ex2(s * sc + co)
+      float L = 0.f, sd = 0.f;   // row sums over this thread's columns: exponentials; D = E - P
 
-      // valid tile-local columns [clo, chi] of query position q in key tile t (both monotone in q)
-      auto col_lo = [&](int t, int q) { return max(q - hw - ((int)p.k_pos0 + T.j0 + t * KT), 0); };
-      auto col_hi = [&](int t, int q) {
-        const int gk0 = (int)p.k_pos0 + T.j0 + t * KT;
-        return min(min(q - hw + p.w - 1 - gk0, T.len_b - 1 - gk0), KT - 1);
+      // Visibility of this thread's 32 columns in key tile t: bit k of vis = query row gi sees column c0 + k
+      // (the columns a row sees form one interval); none / all: no / every row of this warp sees the whole chunk.
+      struct Geo {
+        uint32_t vis;
+        bool none, all;
       };
-      // Software pipeline over key tiles: A(t+1) (exponentials of S) runs while the
-      // tensor core computes P(t); B(t) then forms D(t).
+      auto geometry = [&](int t) {
+        const int gk0 = (int)p.k_pos0 + T.j0 + t * KT + c0;            // global position of column c0
+        const int lo = max(gi - hw - gk0, 0);
+        const int hi = min(min(gi - hw + p.w - 1, T.len_b - 1) - gk0, 31);
+        Geo G;
+        G.vis = hi >= lo ? (0xFFFFFFFFu >> (31 - (hi - lo))) << lo : 0u;
+        G.none = __all_sync(0xFFFFFFFFu, G.vis == 0u);
+        G.all = __all_sync(0xFFFFFFFFu, G.vis == 0xFFFFFFFFu);
+        return G;
+      };
+      Geo Gb, Ga;   // geometry of the tile phase B works on / phase A works on
+      // Software pipeline over key tiles: A(t+1) (exponentials of S, written back over S) runs while the
+      // tensor core subtracts P(t) from the buffer of tile t; B(t) then packs D(t).
       for (int t = -1; t < nt; ++t) {
         if (t + 1 < nt) {
-          // A: S(t+1) -> masked exponentials (kept packed), row sum L
-          const int u = t + 1, gg = gk + u, s = gg & 1;
-          const int clo = col_lo(u, gi), chi = col_hi(u, gi);
-          const int wlo = col_lo(u, gi_first), wlo_max = col_lo(u, gi_last);
-          const int whi_min = col_hi(u, gi_first), whi = col_hi(u, gi_last);
+          // A: S(t+1) -> E = exp(tau S - pls) in place (fp32), row sum L
+          const int gg = gk + t + 1, s = gg & 1;
+          Ga = geometry(t + 1);
           mbar_wait(bars + B_SFULL + s, (gg >> 1) & 1, a.status, 35);
           tc_fence_after_sync();
+          SBL_MARK(tr && t + 1 < 3, trb + 5 + 4 * (t + 1));
+          if (!Ga.none) {   // a chunk nobody sees is left as it is: B writes zeros for it
+            const uint32_t tcol = lane_base + T_BUF + s * 128 + c0;
+            uint32_t rs[32];
+            tmem_ld32(tcol, rs);
+            tmem_ld_wait();
+            float2 l2 = make_float2(0.f, 0.f);
+            if (Ga.all) {
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            const int c0 = PW * cq + 32 * c;
-            if (c0 + 31 < wlo || c0 > whi) {   // no row of this warp sees these 32 keys
+              for (int j = 0; j < 16; ++j) {
+                const float2 x =
+                    fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
+                const float2 e = make_float2(ex2(x.x), ex2(x.y));
+                l2 = add2(l2, e);
+                rs[2 * j] = __float_as_uint(e.x);
+                rs[2 * j + 1] = __float_as_uint(e.y);
+              }
+            } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) En[16 * c + j] = 0u;
-              continue;
-            }
-            float l0 = 0.f, l1 = 0.f;
-            const bool all_visible = c0 >= wlo_max && c0 + 31 <= whi_min;   // every row of this warp sees all 32 keys
-            const unsigned span = (unsigned)(chi - clo);
-#pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {      // two halves of 16 columns keep the register footprint small
-              uint32_t rs[16];
-              tmem_ld16(lane_base + T_BUF + s * 128 + c0 + 16 * hc, rs);
-              tmem_ld_wait();
-              if (all_visible) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const float e0 = ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co));
-                  const float e1 = ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co));
-                  l0 += e0;
-                  l1 += e1;
-                  En[16 * c + 8 * hc + j] = pack_bf16(e0, e1);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const int col = c0 + 16 * hc + 2 * j;
-                  const bool ok0 = chi >= clo && (unsigned)(col - clo) <= span;
-                  const bool ok1 = chi >= clo && (unsigned)(col + 1 - clo) <= span;
-                  const float e0 = ok0 ? ex2(fmaf(__uint_as_float(rs[2 * j]), sc, co)) : 0.f;
-                  const float e1 = ok1 ? ex2(fmaf(__uint_as_float(rs[2 * j + 1]), sc, co)) : 0.f;
-                  l0 += e0;
-                  l1 += e1;
-                  En[16 * c + 8 * hc + j] = pack_bf16(e0, e1);
-                }
+              for (int j = 0; j < 16; ++j) {
+                const float2 x =
+                    fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
+                const float2 e = make_float2(keep_if_bit(ex2(x.x), Ga.vis, 2 * j), keep_if_bit(ex2(x.y), Ga.vis, 2 * j + 1));
+                l2 = add2(l2, e);
+                rs[2 * j] = __float_as_uint(e.x);
+                rs[2 * j + 1] = __float_as_uint(e.y);
               }
             }
-            L += l0 + l1;
+            tmem_st32(tcol, rs);
+            L += l2.x + l2.y;
+            tmem_st_wait();
           }
           tc_fence_before_sync();
           mbar_arrive(bars + B_ADONE + s);
+          SBL_MARK(tr && t + 1 < 3, trb + 6 + 4 * (t + 1));
         }
         if (t >= 0) {
-          // B: P(t) -> D = E - P (packed bf16 into tensor memory), row sum dps
+          // B: D(t) = E - P (fp32, left by the tensor core) -> masked, packed bf16 into tensor memory, row sum
           const int gg = gk + t, s = gg & 1;
-          const int clo = col_lo(t, gi), chi = col_hi(t, gi);
-          const int wlo = col_lo(t, gi_first), wlo_max = col_lo(t, gi_last);
-          const int whi_min = col_hi(t, gi_first), whi = col_hi(t, gi_last);
           mbar_wait(bars + B_PFULL + s, (gg >> 1) & 1, a.status, 36);
           if (gg >= 1) mbar_wait(bars + B_DFREE, (gg - 1) & 1, a.status, 37);
           tc_fence_after_sync();
+          SBL_MARK(tr && t < 3, trb + 7 + 4 * t);
+          const uint32_t tcol = lane_base + T_BUF + s * 128 + c0;
+          float2 d2 = make_float2(0.f, 0.f);
+          uint32_t dpk[16];
+          if (Gb.none) {
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            const int c0 = PW * cq + 32 * c;
-            const bool none_visible = c0 + 31 < wlo || c0 > whi;
-            const bool all_visible = c0 >= wlo_max && c0 + 31 <= whi_min;
-            const unsigned span = (unsigned)(chi - clo);
-            float d0 = 0.f, d1 = 0.f;
+            for (int j = 0; j < 16; ++j) dpk[j] = 0u;
+          } else {
+            uint32_t rp[32];
+            tmem_ld32(tcol, rp);
+            tmem_ld_wait();
+            if (Gb.all) {
 #pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
-              uint32_t dpk[8];
-              if (none_visible) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) dpk[j] = 0u;
-              } else {
-                uint32_t rp[16];
-                tmem_ld16(lane_base + T_BUF + s * 128 + c0 + 16 * hc, rp);
-                tmem_ld_wait();
-                if (all_visible) {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    const float pv0 = __uint_as_float(rp[2 * j]), pv1 = __uint_as_float(rp[2 * j + 1]);
-                    const uint32_t e = Ec[16 * c + 8 * hc + j];
-                    d0 += pv0;
-                    d1 += pv1;
-                    dpk[j] = pack_bf16(bf16_lo(e) - pv0, bf16_hi(e) - pv1);
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    const int col = c0 + 16 * hc + 2 * j;
-                    const bool ok0 = chi >= clo && (unsigned)(col - clo) <= span;
-                    const bool ok1 = chi >= clo && (unsigned)(col + 1 - clo) <= span;
-                    const float pv0 = ok0 ? __uint_as_float(rp[2 * j]) : 0.f;
-                    const float pv1 = ok1 ? __uint_as_float(rp[2 * j + 1]) : 0.f;
-                    const uint32_t e = Ec[16 * c + 8 * hc + j];
-                    d0 += pv0;
-                    d1 += pv1;
-                    dpk[j] = pack_bf16(bf16_lo(e) - pv0, bf16_hi(e) - pv1);
-                  }
-                }
+              for (int j = 0; j < 16; ++j) {
+                const float2 d = make_float2(__uint_as_float(rp[2 * j]), __uint_as_float(rp[2 * j + 1]));
+                d2 = add2(d2, d);
+                dpk[j] = pack_bf16(d.x, d.y);
               }
-              tmem_st8(lane_base + T_D + c0 / 2 + 8 * hc, dpk);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float2 d = make_float2(keep_if_bit(__uint_as_float(rp[2 * j]), Gb.vis, 2 * j),
+                                             keep_if_bit(__uint_as_float(rp[2 * j + 1]), Gb.vis, 2 * j + 1));
+                d2 = add2(d2, d);
+                dpk[j] = pack_bf16(d.x, d.y);
+              }
             }
-            dps += d0 + d1;
           }
+          tmem_st16(lane_base + T_D + c0 / 2, dpk);
+          sd += d2.x + d2.y;
           tmem_st_wait();
           tc_fence_before_sync();
           mbar_arrive(bars + B_BDONE + s);
+          SBL_MARK(tr && t < 3, trb + 8 + 4 * t);
         }
-#pragma unroll
-        for (int j = 0; j < 16 * CH; ++j) Ec[j] = En[j];
+        Gb = Ga;
       }
       // ---- combine the column groups of each row ----
+      // L + max(Z - dps, 1e-24) = max(Z + sum D, L + 1e-24), with sum D = L - dps
       s_xch[tid] = L;
-      s_xch[NSOFT + tid] = dps;
-      s_xch[2 * NSOFT + tid] = (z0 + z1) + (z2 + z3);
+      s_xch[NSOFT + tid] = ((zp.x + zp.y) + (zm.x + zm.y)) + sd;
       asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
-      float Z = 0.f;
+      float ZD = 0.f;
       L = 0.f;
-      dps = 0.f;
 #pragma unroll
       for (int j = 0; j < NCQ; ++j) {
-        const int m8 = (tid & 127) + 128 * j;
-        L += s_xch[m8];
-        dps += s_xch[NSOFT + m8];
-        Z += s_xch[2 * NSOFT + m8];
+        L += s_xch[row + 128 * j];
+        ZD += s_xch[NSOFT + row + 128 * j];
       }
       // ---- epilogue: this thread writes 64/NCQ of the row's 64 outputs ----
+      SBL_MARK(tr, trb + 17);
       mbar_wait(bars + B_DONE, it & 1, a.status, 38);
       tc_fence_after_sync();
-      const float inv = 1.f / (L + fmaxf(Z - dps, 1e-24f));
+      SBL_MARK(tr, trb + 18);
+      const float inv = 1.f / fmaxf(ZD, L + 1e-24f);
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + T.b * p.o_stride_b + T.h * p.o_stride_h +
                             (int64_t)(T.i0 + row) * p.o_stride_t + OW * cq;
-#pragma unroll
-      for (int og = 0; og < OW / 16; ++og) {
+      {
         // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
         uint32_t ro[16];
-        tmem_ld16(lane_base + T_O + OW * cq + 16 * og, ro);
+        tmem_ld16(lane_base + T_O + OW * cq, ro);
         tmem_ld_wait();
         uint32_t o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
         if (row < T.nq) {
-          reinterpret_cast<uint4*>(orow + 16 * og)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          reinterpret_cast<uint4*>(orow + 16 * og)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          reinterpret_cast<uint4*>(orow)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          reinterpret_cast<uint4*>(orow)[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
       // O has been read: the next query tile's phi(Q) arrival (B_PHIQ) releases the low-rank MMA that overwrites it
+      SBL_MARK(tr, trb + 19);
       gk += nt;
     }
   }
@@ -1275,3 +1373,9 @@ cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cu
 }
 
 }  // namespace sbl
+
+#ifdef SBL_TRACE
+extern "C" int sbl_trace_fetch(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, sbl::g_band_trace, sizeof(long long) * 160 * 96);
+}
+#endif
