@@ -71,6 +71,12 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return d;
 }
 
+// One arrival for the whole warp, after every lane's earlier accesses are ordered before it.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
 // v if bit k of mask is set, else 0 (two instructions: shift the bit into the sign, select on the sign)
 __device__ __forceinline__ float keep_if_bit(float v, uint32_t mask, int k) {
   float d;
@@ -251,6 +257,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
                "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem, int x, int y, int z, int u) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z), "r"(u)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -555,14 +568,14 @@ __device__ long long g_band_trace[160][96];
   do {                                                         \
     if (cond) g_band_trace[blockIdx.x][slot] = clock64();      \
   } while (0)
-constexpr int kTraceIt = 5;
+constexpr int kTraceIt = 20;
 #else
 #define SBL_MARK(cond, slot) \
   do {                       \
   } while (0)
 #endif
 struct BandArgs {
-  CUtensorMap tm_q, tm_k, tm_v, tm_w, tm_phik, tm_kv;
+  CUtensorMap tm_q, tm_k, tm_v, tm_w, tm_phik, tm_kv, tm_out;
   SblParams p;
   const float* beta;
   const float* ksum;
@@ -597,18 +610,19 @@ enum {
   B_W,           // Wt landed                          (per query tile)
   B_KV,          // KV landed                          (per query tile)
   B_UQ,          // U = Q Wt^T computed                (per query tile)
-  B_PHIQ,        // phi(Q) stored, O read              (per query tile, NSOFT arrivals)
+  B_PHIQ,        // phi(Q) stored, O read              (per query tile, one arrival per softmax warp)
   B_DONE,        // all MMAs of the query tile done    (per query tile)
-  B_QFREE,       // Q buffer reusable                  (per query tile, 1 + NSOFT arrivals)
+  B_QFREE,       // Q buffer reusable                  (per query tile, 1 + one per softmax warp)
   B_WFREE,       // Wt/KV buffer reusable              (per query tile)
   B_DFREE,       // D consumed by O += D V             (per key tile)
   B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY,              // per key tile, single buffers
   B_PKFULL, B_PKEMPTY = B_PKFULL + 2,                // [2] per key tile, by ring slot
   B_SFULL = B_PKEMPTY + 2,                           // [2] by buffer
-  B_ADONE = B_SFULL + 2,                             // [2] NSOFT arrivals
+  B_ADONE = B_SFULL + 2,                             // [2] one arrival per softmax warp
   B_PFULL = B_ADONE + 2,                             // [2]
-  B_BDONE = B_PFULL + 2,                             // [2] NSOFT arrivals
+  B_BDONE = B_PFULL + 2,                             // [2] one arrival per softmax warp
   B_SISS = B_BDONE + 2,                              // S of a third or later key tile has been issued (orders P behind it)
+  B_OFULL,                                           // output tile staged in shared memory (one arrival per softmax warp)
   B_COUNT
 };
 static_assert(B_COUNT <= 32, "one barrier per lane of the initialising warp");
@@ -692,8 +706,9 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
 
   if (warp == WP + 1) {
     if (lane < B_COUNT) {
-      const bool soft = lane == B_PHIQ || lane == B_ADONE || lane == B_ADONE + 1 || lane == B_BDONE || lane == B_BDONE + 1;
-      mbar_init(bars + lane, lane == B_QFREE ? NSOFT + 1 : (soft ? NSOFT : 1));
+      const bool soft = lane == B_PHIQ || lane == B_OFULL || lane == B_ADONE || lane == B_ADONE + 1 || lane == B_BDONE || lane == B_BDONE + 1;
+      // the softmax warps arrive once per warp
+      mbar_init(bars + lane, lane == B_QFREE ? WP + 1 : (soft ? WP : 1));
     }
     fence_mbar_init();
   }
@@ -708,6 +723,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   // column 0; keeping the base a compile-time constant keeps every MMA operand uniform.
   constexpr uint32_t tb = 0;
   if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 40);
+  SBL_MARK(tid == 0, 70);
 
   if (warp == WP) {
     // ---------------- producer (whole warp waits, one lane issues) ----------------
@@ -719,6 +735,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       prefetch_tmap(&a.tm_w);
       prefetch_tmap(&a.tm_phik);
       prefetch_tmap(&a.tm_kv);
+      prefetch_tmap(&a.tm_out);
     }
     int gk = 0;   // key tiles loaded so far
     PkTrack pk;
@@ -739,6 +756,18 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         mbar_expect_tx(bars + B_W, 16384);
         tma_load_2d(smem + OFF_KV, &a.tm_w, bars + B_W, 0, 0);
       }
+    };
+    // The softmax warps stage a finished output tile in the V buffer (free once the tile's last O += D V has
+    // run); one bulk store writes it out.  The next V load waits until the store has read the buffer.
+    int o_i0 = 0, o_h = 0, o_b = 0;
+    auto store_out = [&](int it2) {
+      mbar_wait(bars + B_OFULL, it2 & 1, a.status, 45);
+      if (leader) {
+        tma_store_4d(&a.tm_out, smem + OFF_V, 0, o_i0, o_h, o_b);
+        tma_store_commit();
+        tma_store_wait_read0();
+      }
+      __syncwarp();
     };
     load_qw(0);
     for (int it = 0; it < n_it; ++it, cur.next(a)) {
@@ -787,18 +816,31 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           }
           pk.used(ps);
         }
+        // V(0) is not needed before the first O += D V; its buffer holds the previous tile's staged output
+        // until that tile's epilogue, which must not hold up the K tile S(1) is waiting for
         if (t == 0) {
-          load_v(0);
           load_kv();
-        } else if (t >= 2) {
+        } else if (t == 1) {
+          if (it >= 1) store_out(it - 1);
+          load_v(0);
+        } else {
           load_v(t - 1);
         }
       }
       if (T.nt == 0) load_kv();
+      if (T.nt <= 1) {
+        if (it >= 1) store_out(it - 1);
+        if (T.nt == 1) load_v(0);
+      }
+      o_i0 = T.i0;
+      o_h = T.h;
+      o_b = T.b;
       load_qw(it + 1);
       if (T.nt >= 2) load_v(T.nt - 1);
       gk += T.nt;
     }
+    store_out(n_it - 1);
+    if (leader) tma_store_wait_all();
     __syncwarp();
   } else if (warp == WP + 1) {
     // ---------------- MMA issuer A: U, S, low-rank, O (whole warp waits, one lane issues) ----------------
@@ -979,7 +1021,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       mbar_wait(bars + B_Q, it & 1, a.status, 33);
       SBL_MARK(tr, trb + 1);
       s_sq[tid] = quarter_row_sumsq_sw128(smem + OFF_Q, row, cq);
-      mbar_arrive(bars + B_QFREE);
+      warp_arrive(bars + B_QFREE, lane);
       asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
       const float qn2 = (s_sq[row] + s_sq[128 + row]) + (s_sq[256 + row] + s_sq[384 + row]);
       const float g = 0.5f * p.softmax_temp * qn2;
@@ -1018,7 +1060,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         tmem_st_wait();
       }
       tc_fence_before_sync();
-      mbar_arrive(bars + B_PHIQ);
+      warp_arrive(bars + B_PHIQ, lane);
       SBL_MARK(tr, trb + 4);
 
       const float pls = (-g + M - half_log_m) + beta;               // query log-scale + key log-scale
@@ -1085,7 +1127,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
             tmem_st_wait();
           }
           tc_fence_before_sync();
-          mbar_arrive(bars + B_ADONE + s);
+          warp_arrive(bars + B_ADONE + s, lane);
           SBL_MARK(tr && t + 1 < 3, trb + 6 + 4 * (t + 1));
         }
         if (t >= 0) {
@@ -1126,7 +1168,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           sd += d2.x + d2.y;
           tmem_st_wait();
           tc_fence_before_sync();
-          mbar_arrive(bars + B_BDONE + s);
+          warp_arrive(bars + B_BDONE + s, lane);
           SBL_MARK(tr && t < 3, trb + 8 + 4 * t);
         }
         Gb = Ga;
@@ -1149,10 +1191,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       tc_fence_after_sync();
       SBL_MARK(tr, trb + 18);
       const float inv = 1.f / fmaxf(ZD, L + 1e-24f);
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + T.b * p.o_stride_b + T.h * p.o_stride_h +
-                            (int64_t)(T.i0 + row) * p.o_stride_t + OW * cq;
       {
-        // tensor-memory loads are warp-wide: every lane runs them, only the store is predicated
+        // tensor-memory loads are warp-wide: every lane runs them
         uint32_t ro[16];
         tmem_ld16(lane_base + T_O + OW * cq, ro);
         tmem_ld_wait();
@@ -1160,10 +1200,14 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           o[j] = pack_bf16(__uint_as_float(ro[2 * j]) * inv, __uint_as_float(ro[2 * j + 1]) * inv);
-        if (row < T.nq) {
-          reinterpret_cast<uint4*>(orow)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          reinterpret_cast<uint4*>(orow)[1] = make_uint4(o[4], o[5], o[6], o[7]);
-        }
+        // Stage the 32 bytes of this thread in the V buffer (the tile's last O += D V has run), laid out as
+        // the output tensor map expects: 128-byte rows, 16-byte chunks XORed with row % 8.  The producer
+        // warp writes the tile out with one bulk store, which clips rows past the end of the sequence.
+        uint8_t* srow = smem + OFF_V + row * 128;
+        *reinterpret_cast<uint4*>(srow + (((2 * cq) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(srow + (((2 * cq + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        fence_async_smem();
+        warp_arrive(bars + B_OFULL, lane);
       }
       // O has been read: the next query tile's phi(Q) arrival (B_PHIQ) releases the low-rank MMA that overwrites it
       SBL_MARK(tr, trb + 19);
@@ -1172,6 +1216,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   }
   tc_fence_before_sync();
   __syncthreads();
+  SBL_MARK(tid == 0, 71);
   if (warp == WP) {
     __syncwarp();
     tmem_dealloc(tb, 512);
@@ -1328,7 +1373,8 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   BandArgs a{};
   if (!map_bthe(&a.tm_q, p.q, p.B, p.T, p.H, p.q_stride_b, p.q_stride_t, p.q_stride_h, 128) ||
       !map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
-      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128))
+      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128) ||
+      !map_bthe(&a.tm_out, p.out, p.B, p.T, p.H, p.o_stride_b, p.o_stride_t, p.o_stride_h, 128))
     return cudaErrorInvalidValue;
   {
     const uint64_t dims[2] = {(uint64_t)kE, (uint64_t)kR};
