@@ -477,9 +477,13 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
           uint32_t p1[16], p2[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float u0 = __uint_as_float(r[2 * j]) * kLog2e, u1 = __uint_as_float(r[2 * j + 1]) * kLog2e;
-            p1[j] = live ? pack_bf16(ex2(u0 + off), ex2(u1 + off)) : 0u;
-            p2[j] = live ? pack_bf16(ex2(off - u0), ex2(off - u1)) : 0u;
+            constexpr float2 lp = {kLog2e, kLog2e}, lm = {-kLog2e, -kLog2e};
+            const float2 u = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            const float2 ap = fma2(u, lp, make_float2(off, off)), am = fma2(u, lm, make_float2(off, off));
+            const float2 ep = make_float2(ex2(ap.x), ex2(ap.y));
+            const float2 em = make_float2(ex2(am.x), ex2(am.y));
+            p1[j] = live ? pack_bf16(ep.x, ep.y) : 0u;
+            p2[j] = live ? pack_bf16(em.x, em.y) : 0u;
           }
           if (!plain && row < a.S) {
 #pragma unroll
@@ -569,7 +573,19 @@ __device__ long long g_band_trace[160][96];
     if (cond) g_band_trace[blockIdx.x][slot] = clock64();      \
   } while (0)
 constexpr int kTraceIt = 20;
+__device__ __forceinline__ long long trace_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define SBL_MARK_NS(cond, slot)                                \
+  do {                                                         \
+    if (cond) g_band_trace[blockIdx.x][slot] = trace_ns();     \
+  } while (0)
 #else
+#define SBL_MARK_NS(cond, slot) \
+  do {                          \
+  } while (0)
 #define SBL_MARK(cond, slot) \
   do {                       \
   } while (0)
@@ -724,6 +740,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   constexpr uint32_t tb = 0;
   if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 40);
   SBL_MARK(tid == 0, 70);
+  SBL_MARK_NS(tid == 0, 72);
 
   if (warp == WP) {
     // ---------------- producer (whole warp waits, one lane issues) ----------------
@@ -1048,7 +1065,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
           for (int j = 0; j < 8; ++j) {
             const float2 u = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
             const float2 ap = fma2(u, lp, mo2), am = fma2(u, lm, mo2);
-            const float2 ep = make_float2(ex2(ap.x), ex2(ap.y)), em = make_float2(ex2(am.x), ex2(am.y));
+            const float2 ep = make_float2(ex2(ap.x), ex2(ap.y));
+            const float2 em = make_float2(ex2(am.x), ex2(am.y));
             p1[j] = pack_bf16(ep.x, ep.y);
             p2[j] = pack_bf16(em.x, em.y);
             zp = fma2(ep, *reinterpret_cast<const float2*>(s_ksum + f0 + 2 * j), zp);
@@ -1116,7 +1134,8 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
               for (int j = 0; j < 16; ++j) {
                 const float2 x =
                     fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
-                const float2 e = make_float2(keep_if_bit(ex2(x.x), Ga.vis, 2 * j), keep_if_bit(ex2(x.y), Ga.vis, 2 * j + 1));
+                const float2 ee = make_float2(ex2(x.x), ex2(x.y));
+                const float2 e = make_float2(keep_if_bit(ee.x, Ga.vis, 2 * j), keep_if_bit(ee.y, Ga.vis, 2 * j + 1));
                 l2 = add2(l2, e);
                 rs[2 * j] = __float_as_uint(e.x);
                 rs[2 * j + 1] = __float_as_uint(e.y);
@@ -1217,6 +1236,7 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   tc_fence_before_sync();
   __syncthreads();
   SBL_MARK(tid == 0, 71);
+  SBL_MARK_NS(tid == 0, 73);
   if (warp == WP) {
     __syncwarp();
     tmem_dealloc(tb, 512);
