@@ -340,7 +340,7 @@ def main():
         elem = 2 if dtype == 'bf16' else 4
         peak_tf = peaks['bf16_tflops']
         achieved = band_flops / (band_ms * 1e-3) / 1e12
-        launches_per_step = 7 if tensor_path else 8
+        launches_per_step = 5 if tensor_path else 8
         # dram__bytes_read.sum + dram__bytes_write.sum of one tc_band_kernel launch, from the ncu capture summarised
         # in profiles/tc_band_kernel_B2_H4_N16384.md (quarter batch: 126.2 MB), scaled by the (batch x head) count
         band_traffic = (126.2e6 * (B * H) / 8.0) if (tensor_path and N == 16384) else None

@@ -230,10 +230,13 @@ int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, voi
   float* ksum = reinterpret_cast<float*>(base + ws.ksum);
   cudaError_t e;
   if (ws.tensor) {
-    if ((e = tc_prepare_projection(*p, ws, base, st, true)) != cudaSuccess) return cuda_fail(e, "prepare projection");
-    if ((e = tc_key_logscale_bound(*p, ws, base, beta, st)) != cudaSuccess) return cuda_fail(e, "key logscale bound");
-    if ((e = tc_key_summary(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "key summary");
-    if ((e = tc_band(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "band forward");
+    // five launches: projection (+ log-scale reset), log-scale bound, keys, combine (+ bf16 KV), band
+    if ((e = tc_prepare_projection(*p, ws, base, st, true, beta)) != cudaSuccess)
+      return cuda_fail(e, "prepare projection");
+    if ((e = tc_key_logscale_bound(*p, ws, base, beta, st, true)) != cudaSuccess)
+      return cuda_fail(e, "key logscale bound");
+    if ((e = tc_key_summary(*p, ws, base, beta, kv, ksum, st, true)) != cudaSuccess) return cuda_fail(e, "key summary");
+    if ((e = tc_band(*p, ws, base, beta, kv, ksum, st, true)) != cudaSuccess) return cuda_fail(e, "band forward");
     return check_device_status(ws, base, st);
   }
   float* phik = reinterpret_cast<float*>(base + ws.phik);

@@ -57,15 +57,18 @@ cudaError_t f32_attention_weights(const SblParams& p, const Workspace& ws, char*
 // ---- tensor-core path (bf16 storage, tcgen05 + TMA), sbl_tc.cu ----
 bool tc_supported(const SblParams& p);
 // reset_status: clear the device status words (first stage of a call sequence)
+// beta_fill: when given, the B*H key log-scales there are reset to -inf by the same launch
 cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
-                                  bool reset_status);
+                                  bool reset_status, float* beta_fill = nullptr);
 cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
 // one-pass upper bound on the key log-scale (valid stabiliser when eps = 0); used by the fused forward
-cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st);
+cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st,
+                                  bool beta_is_reset = false);
+// also_bf16: also leave KV in bf16 in the workspace, where a tc_band call with kv16_ready picks it up
 cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta,
-                           float* kv, float* ksum, cudaStream_t st);
+                           float* kv, float* ksum, cudaStream_t st, bool also_bf16 = false);
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
-                    const float* kv, const float* ksum, cudaStream_t st);
+                    const float* kv, const float* ksum, cudaStream_t st, bool kv16_ready = false);
 // copies the device status word to *host_status and synchronises the stream
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st);
 

@@ -121,8 +121,11 @@ __device__ __forceinline__ float row_sumsq_sw128(const uint8_t* tile, int row) {
 // One block of 1024 threads, 8 per projection row: sqrt(tau)*W in fp32 and bf16, the largest row
 // norm of the bf16 copy (bound on |u_f| / |x| used as the query feature stabiliser), status reset.
 __global__ void __launch_bounds__(1024) tc_prep_kernel(const float* W, float c, float* wt32, __nv_bfloat16* wt16,
-                                                       int r, int E, int* status, float* wmax, int reset_status) {
+                                                       int r, int E, int* status, float* wmax, int reset_status,
+                                                       float* beta_fill, int n_beta) {
   __shared__ float red[32];
+  // the fused forward lets this launch also reset the key log-scales (they are formed by atomic max)
+  for (int i = threadIdx.x; i < n_beta; i += blockDim.x) beta_fill[i] = -INFINITY;
   float mx = 0.f;
   for (int f0 = 0; f0 < r; f0 += 128) {
     const int f = f0 + threadIdx.x / 8, part = threadIdx.x % 8;
@@ -195,7 +198,8 @@ __global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* 
 }
 
 // kv (BH,256,64), ksum (BH,256) = sum over the splits of the per-CTA partial summaries
-__global__ void tc_combine_kernel(const float* partial, int nsplit, int BH, float* kv, float* ksum) {
+__global__ void tc_combine_kernel(const float* partial, int nsplit, int BH, float* kv, float* ksum,
+                                  __nv_bfloat16* kv16) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over BH * 256 * 20 float4 groups
   if (i >= (int64_t)BH * kM * (kPartialLd / 4)) return;
   const int g = (int)(i % (kPartialLd / 4));
@@ -207,8 +211,15 @@ __global__ void tc_combine_kernel(const float* partial, int nsplit, int BH, floa
     const float4 v = *reinterpret_cast<const float4*>(partial + ((bh * nsplit + k) * kM + f) * kPartialLd + 4 * g);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
-  if (g < 16) *reinterpret_cast<float4*>(kv + bf * kE + 4 * g) = acc;
-  else ksum[bf] = acc.x;
+  if (g < 16) {
+    *reinterpret_cast<float4*>(kv + bf * kE + 4 * g) = acc;
+    if (kv16) {   // the band kernel's bf16 operand, when the caller goes straight on to the band stage
+      const uint2 h = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+      *reinterpret_cast<uint2*>(kv16 + bf * kE + 4 * g) = h;
+    }
+  } else {
+    ksum[bf] = acc.x;
+  }
 }
 
 __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64_t n) {
@@ -1343,10 +1354,10 @@ bool tc_supported(const SblParams& p) {
 }
 
 cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
-                                  bool reset_status) {
+                                  bool reset_status, float* beta_fill) {
   const TcLayout l = tc_layout(p, ws, base);
   tc_prep_kernel<<<1, 1024, 0, st>>>(p.W, (float)sqrt((double)p.softmax_temp), l.wt32, l.wt16, p.r, p.E, l.status,
-                                    l.wmax, reset_status ? 1 : 0);
+                                    l.wmax, reset_status ? 1 : 0, beta_fill, beta_fill ? p.B * p.H : 0);
   return cudaGetLastError();
 }
 
@@ -1358,12 +1369,15 @@ cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base,
   return launch_keys<true>(p, ws, base, nullptr, beta, st);
 }
 
-cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st) {
+cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st,
+                                  bool beta_is_reset) {
   const TcLayout l = tc_layout(p, ws, base);
   const int bh = p.B * p.H;
-  tc_fill_kernel<<<(unsigned)div_up(bh, 256), 256, 0, st>>>(beta, -INFINITY, bh);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  if (!beta_is_reset) {
+    tc_fill_kernel<<<(unsigned)div_up(bh, 256), 256, 0, st>>>(beta, -INFINITY, bh);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
   const int rows = p.sum_hi - p.sum_lo;
   if (rows <= 0) return cudaSuccess;
   dim3 grid((unsigned)div_up(rows, 512), (unsigned)bh);
@@ -1374,22 +1388,26 @@ cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char*
 }
 
 cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta, float* kv,
-                           float* ksum, cudaStream_t st) {
+                           float* ksum, cudaStream_t st, bool also_bf16) {
   cudaError_t e = launch_keys<false>(p, ws, base, beta, nullptr, st);
   if (e != cudaSuccess) return e;
   const int bh = p.B * p.H;
   const int64_t n = (int64_t)bh * kM * (kPartialLd / 4);
-  tc_combine_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(tc_layout(p, ws, base).partial, ws.nsplit, bh, kv, ksum);
+  const TcLayout l = tc_layout(p, ws, base);
+  tc_combine_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(l.partial, ws.nsplit, bh, kv, ksum,
+                                                             also_bf16 ? l.kv16 : nullptr);
   return cudaGetLastError();
 }
 
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta, const float* kv,
-                    const float* ksum, cudaStream_t st) {
+                    const float* ksum, cudaStream_t st, bool kv16_ready) {
   const TcLayout l = tc_layout(p, ws, base);
-  const int64_t nkv = (int64_t)p.B * p.H * kM * kE;
-  tc_kv_to_bf16_kernel<<<(unsigned)div_up(nkv, 256), 256, 0, st>>>(kv, l.kv16, nkv);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  cudaError_t e = cudaSuccess;
+  if (!kv16_ready) {
+    const int64_t nkv = (int64_t)p.B * p.H * kM * kE;
+    tc_kv_to_bf16_kernel<<<(unsigned)div_up(nkv, 256), 256, 0, st>>>(kv, l.kv16, nkv);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  }
   BandArgs a{};
   if (!map_bthe(&a.tm_q, p.q, p.B, p.T, p.H, p.q_stride_b, p.q_stride_t, p.q_stride_h, 128) ||
       !map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
