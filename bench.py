@@ -342,8 +342,8 @@ def main():
         achieved = band_flops / (band_ms * 1e-3) / 1e12
         launches_per_step = 5 if tensor_path else 8
         # dram__bytes_read.sum + dram__bytes_write.sum of one tc_band_kernel launch, from the ncu capture summarised
-        # in profiles/tc_band_kernel_B2_H4_N16384.md (quarter batch: 126.2 MB), scaled by the (batch x head) count
-        band_traffic = (126.2e6 * (B * H) / 8.0) if (tensor_path and N == 16384) else None
+        # in profiles/tc_band_kernel_B2_H4_N16384.md (quarter batch: 159.4 MB), scaled by the (batch x head) count
+        band_traffic = (159.4e6 * (B * H) / 8.0) if (tensor_path and N == 16384) else None
         line = dict(
             metric=METRIC, value=value, unit='tokens/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=ms_per_step, higher_is_better=True, scaling='weak', vs_baseline=None,
