@@ -369,6 +369,27 @@ def main():
                                   hbm_gbs=4 * th * d * elem / (ms_per_step * 1e-3) / 1e9,
                                   hbm_peak_gbs=peaks['hbm_gbs']),
         )
+        if not tensor_path:
+            # The generic path computes in fp32 on the FMA pipe: its ceiling is the FP32 peak, not the tensor peak.
+            # Measured here with an fp32 (TF32 off) cuBLAS GEMM, 8192^3, best of 5.
+            tf32 = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = False
+            ga = torch.randn(8192, 8192, device=dev)
+            gb = torch.randn(8192, 8192, device=dev)
+            best = float('inf')
+            for _ in range(6):
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record()
+                torch.matmul(ga, gb)
+                g1.record()
+                torch.cuda.synchronize(dev)
+                best = min(best, g0.elapsed_time(g1))
+            torch.backends.cuda.matmul.allow_tf32 = tf32
+            del ga, gb
+            fp32_peak = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+            line['roofline']['fp32_peak_tflops'] = fp32_peak
+            line['roofline']['frac_of_fp32_peak'] = achieved / fp32_peak
+            line['roofline_forward']['frac_of_fp32_peak'] = line['roofline_forward']['achieved'] / fp32_peak
         if world == 1 and not args.no_cpu_baseline:
             from oracle import sblocal_oracle as so
             cores = os.cpu_count() or 1

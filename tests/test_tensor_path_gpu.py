@@ -113,3 +113,24 @@ def test_sequence_shards_on_one_gpu(chunks, sbl_lib):
         p.check_status(workspace=x)
     out = torch.cat(outs, dim=1).float().cpu()
     assert so.rel_err(out, ref) <= TOL_BF16
+
+
+def test_strided_output_is_clipped(sbl_lib):
+    """The output tile goes out through one bulk tensor store per 128 queries: a caller-provided output that is a
+    strided view (every other row of a larger buffer, T not a multiple of 128) must receive exactly its T rows and
+    nothing else may be touched."""
+    from fly_b200 import ops
+    B, T, H, E, w = 2, 333, 2, 64, 256
+    q, k, v, W = _inputs(B, T, T, H, seed=21)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
+    sentinel = 7.0
+    big = torch.full((B, 2 * T + 5, H, E), sentinel, dtype=torch.bfloat16, device='cuda')
+    out_view = big[:, 0:2 * T:2]                      # rows 0, 2, ..., 2T-2
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), w, None, 0.0, None, out_view)
+    out = pr.forward()
+    pr.check_status()
+    assert out.data_ptr() == out_view.data_ptr()
+    assert so.rel_err(out.float().cpu(), ref) <= TOL_BF16
+    untouched = torch.ones(2 * T + 5, dtype=torch.bool)
+    untouched[0:2 * T:2] = False
+    assert (big[:, untouched.cuda()] == sentinel).all()
