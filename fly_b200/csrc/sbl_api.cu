@@ -286,6 +286,19 @@ int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes
   return SBL_OK;
 }
 
+int sbl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!workspace || workspace_bytes < 256) return fail(SBL_ERR_INVALID_ARGUMENT, "self-test needs a 256-byte workspace");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0)
+    return fail(SBL_ERR_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
+  int host = 0;
+  cudaError_t e = tc_wait_selftest(static_cast<int*>(workspace), &host, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_fail(e, "wait self-test");
+  if (host != 0)
+    return fail(SBL_ERR_DEVICE_STATUS, "a bounded wait ran out inside a kernel (wait site %d); results are invalid",
+                host);
+  return SBL_OK;
+}
+
 // The two feature-map entry points always run the fp32 generic kernels: they
 // exist to compare phi(Q), phi(K) and their log-scales with the reference's
 // softmax_kernel element by element.

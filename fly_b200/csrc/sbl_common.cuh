@@ -69,6 +69,8 @@ cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, 
                            float* kv, float* ksum, cudaStream_t st, bool also_bf16 = false);
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta,
                     const float* kv, const float* ksum, cudaStream_t st, bool kv16_ready = false);
+// runs a kernel whose only wait can never be satisfied; *host_status receives the recorded wait site (99)
+cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t st);
 // copies the device status word to *host_status and synchronises the stream
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st);
 

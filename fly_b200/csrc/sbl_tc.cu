@@ -1450,6 +1450,27 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   return cudaGetLastError();
 }
 
+// One warp waits on a barrier that nothing arrives on: the bounded wait must run out, record its site and
+// let the kernel end normally (used to check the mechanism every other device-side wait relies on).
+__global__ void tc_wait_selftest_kernel(int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    *status = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  mbar_wait(&bar, 0, status, 99);
+}
+
+cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t st) {
+  tc_wait_selftest_kernel<<<1, 32, 0, st>>>(device_status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if ((e = cudaMemcpyAsync(host_status, device_status, sizeof(int), cudaMemcpyDeviceToHost, st)) != cudaSuccess) return e;
+  return cudaStreamSynchronize(st);
+}
+
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st) {
   cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, sizeof(int), cudaMemcpyDeviceToHost, st);
   if (e != cudaSuccess) return e;

@@ -58,7 +58,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // already non-zero (another wait of this launch ran out), records `code` in
 // *status and returns false.  The caller keeps going (its results are garbage,
 // but the kernel ends, frees its tensor memory and the host sees the status).
-constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr uint32_t kWaitLimit = 1u << 18;   // about a second: an unsatisfied try_wait comes back after a few microseconds
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;

@@ -152,6 +152,17 @@ int sbl_attention_weights(const SblParams* p, void* workspace, size_t workspace_
 int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes, void* cuda_stream);
 
 /*
+ * Self-test of that mechanism: launches one warp that waits on a barrier
+ * nothing arrives on.  The wait runs out after its iteration limit (about a
+ * second at most), the kernel records the wait site and ends normally, and
+ * the call returns SBL_ERR_DEVICE_STATUS with the site (99) in
+ * sbl_last_error(); the device context stays usable.  SBL_OK would mean the
+ * limit did not work.  workspace: >= 256 bytes of device memory, 16-byte
+ * aligned.  No counterpart in the reference.
+ */
+int sbl_selftest_wait_timeout(void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
  * Feature maps alone, for parity checks against
  * SBPerformerFeatures.forward_queries / forward_keys
  * (feature_maps_sb.py:148-156 -> softmax_kernel :51-82).

@@ -134,3 +134,16 @@ def test_strided_output_is_clipped(sbl_lib):
     untouched = torch.ones(2 * T + 5, dtype=torch.bool)
     untouched[0:2 * T:2] = False
     assert (big[:, untouched.cuda()] == sentinel).all()
+
+
+def test_bounded_wait_runs_out_and_context_survives(sbl_lib):
+    """Every device-side wait has an iteration limit.  The self-test kernel waits on a barrier nothing arrives on:
+    the call must come back with SBL_ERR_DEVICE_STATUS and the recorded wait site, and the next forward on the
+    same device must work."""
+    ws = torch.zeros(256, dtype=torch.uint8, device='cuda')
+    rc = sbl_lib.sbl_selftest_wait_timeout(ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == -5, rc                                # SBL_ERR_DEVICE_STATUS
+    assert b'wait site 99' in sbl_lib.sbl_last_error()
+    q, k, v, W = _inputs(1, 256, 256, 1, seed=3)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 256)
+    assert so.rel_err(_run(q, k, v, W, 256), ref) <= TOL_BF16
