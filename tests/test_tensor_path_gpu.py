@@ -147,3 +147,23 @@ def test_bounded_wait_runs_out_and_context_survives(sbl_lib):
     q, k, v, W = _inputs(1, 256, 256, 1, seed=3)
     ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 256)
     assert so.rel_err(_run(q, k, v, W, 256), ref) <= TOL_BF16
+
+
+def test_bf16_compute_for_fp32_inputs(sbl_lib):
+    """compute_dtype = bfloat16 on the module: fp32 inputs of a supported shape run on the tensor-core kernels and
+    come back as fp32, within the bf16 bound; without it the same inputs stay within the fp32 bound."""
+    from fly_b200 import SBLocalAttention
+    torch.manual_seed(11)
+    B, N, H, E = 2, 784, 1, 64
+    q, k, v = [(torch.randn(B, N, H, E) / E ** 0.25) for _ in range(3)]
+    layer = SBLocalAttention(256, E, 256, softmax_temp=576 ** -0.5).cuda().eval()
+    with torch.no_grad():
+        out32, _ = layer(q.cuda(), k.cuda(), v.cuda())
+        W = layer.feature_map.projection_matrix.float().cpu()
+        ref, _ = so.sblocal_forward(q, k, v, W, 256, 576 ** -0.5)
+        assert so.rel_err(out32.cpu(), ref) <= 1e-4
+        layer.compute_dtype = torch.bfloat16
+        out16, _ = layer(q.cuda(), k.cuda(), v.cuda())
+    assert out16.dtype == torch.float32
+    assert so.rel_err(out16.cpu(), ref) <= TOL_BF16
+    assert not torch.equal(out16, out32)               # it did take the other path
