@@ -91,7 +91,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.FIELDS}',
-                 '--format=csv,noheader,nounits', '-lms', '100'],
+                 '--format=csv,noheader,nounits', '-lms', '50'],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -241,7 +241,18 @@ def main():
             b_.record()
         barrier()
         ms = sum(a_.elapsed_time(b_) for a_, b_ in pairs)
+    if rank == 0 and not args.profile:
+        # nvidia-smi cannot sample faster than the timed region is long (tens of milliseconds): keep the same
+        # step running for 0.6 s more (untimed, results discarded) so that the samples show the clocks under
+        # this load rather than the idle clocks around it
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            for _ in range(20):
+                prob.forward()
+            torch.cuda.synchronize(dev)
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks['sampled_over'] = 'timed region + 0.6 s untimed repeat of the same step, nvidia-smi every 50 ms'
     if args.profile:
         prob.check_status()
         print(f'profile run: {ms / args.steps:.4f} ms per forward (not a benchmark value)')
