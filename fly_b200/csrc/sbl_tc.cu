@@ -5,20 +5,23 @@
 // Everything else takes the generic kernels of sbl_f32.cu.
 //
 // Kernels
-//   prep      sqrt(tau)*W -> bf16 (and fp32), clears the status words
+//   prep      sqrt(tau)*W -> bf16 (and fp32), clears the status words (and, for the fused forward, the log-scales)
+//   key_bound beta = upper bound of the key log-scale from the key norms (fused forward)
 //   keys<MAX> per (split, b*h): streams 128-key tiles; U = K Wt^T on tensor
 //             cores; MAX: running max of (|u| - tau|k|^2/2) -> beta (atomic);
 //             else phi(K) -> bf16 to the workspace and, MN-major, to shared
 //             memory for KV += phi(K)^T [V | 1] (accumulators in tensor memory),
 //             then one partial summary per CTA
-//   combine   (sbl_f32.cu) sums the split partials -> KV, sum phi(K)
-//   band      per (128-query tile, b*h): U = Q Wt^T -> phi(Q) packed bf16 into
-//             tensor memory (the A operand of every phi(Q) product); then per
-//             64-key tile S = Q K^T, P = phi(Q) phi(K)^T (double-buffered in
-//             tensor memory), the softmax warps form
-//             D = exp(tau S - pls) - P (masked to the window and key length) as
-//             packed bf16 in tensor memory, O = phi(Q) KV + sum D V; finally
-//             out = O / (L + max(Z - dps, 1e-24)), written as 128-byte rows.
+//   combine   sums the split partials -> KV (fp32, and bf16 for the band kernel), sum phi(K)
+//   band      persistent, one CTA per SM walking a run of 128-query tiles: U = Q Wt^T ->
+//             phi(Q) packed bf16 into tensor memory (the A operand of every phi(Q)
+//             product); O = phi(Q) KV; then per 128-key tile S = Q K^T into one of
+//             two tensor-memory buffers, the softmax warps write
+//             E = exp(tau S - pls) (masked to the window and key length) back over
+//             S in fp32, the tensor core subtracts P = phi(Q) phi(K)^T from it (same
+//             MMA, A operand negated), the softmax warps pack D = E - P to bf16,
+//             O += D V; finally out = O / max(Z + sum D, L + 1e-24), staged in shared
+//             memory and written by one bulk tensor store per tile.
 //   Everything is kept in "feature units" (divided by e^{pls}, pls = query
 //   log-scale + beta), so the exact and the low-rank terms share one
 //   accumulator and no accumulator is ever rescaled.
