@@ -167,3 +167,21 @@ def test_bf16_compute_for_fp32_inputs(sbl_lib):
     assert out16.dtype == torch.float32
     assert so.rel_err(out16.cpu(), ref) <= TOL_BF16
     assert not torch.equal(out16, out32)               # it did take the other path
+
+
+def test_long_sequence_tensor_vs_generic(sbl_lib):
+    """N = 131072 (the sequence length of the sharded configuration) on one device: the tensor-core kernels against
+    the generic fp32-math kernels on the same bf16 inputs (the CPU oracle would take minutes at this size; the
+    generic kernels are tied to it by the other tests)."""
+    from fly_b200 import ops
+    B, N, H, w = 1, 131072, 2, 256
+    q, k, v, W = _inputs(B, N, N, H, seed=31)
+    q, k, v, W = q.cuda(), k.cuda(), v.cuda(), W.cuda()
+    fast = ops.Problem(q, k, v, W, w)
+    out = fast.forward()
+    fast.check_status()
+    slow = ops.Problem(q, k, v, W, w, generic=True)
+    ref = slow.forward()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    assert so.rel_err(out.float().cpu(), ref.float().cpu()) <= TOL_BF16
