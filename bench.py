@@ -7,15 +7,22 @@ inputs.  Default workload: bf16, B=2, H=16, N=16384, d=64, window 256, m=256
 (the configuration the roofline target is quoted on).  With N>1 GPUs (launched
 by torch.distributed.run, one rank per GPU) every rank runs that batch on its
 own (batch x head) units -- the path has no collective -- so the global batch
-is N times larger (weak scaling).  Rank 0 prints ONE JSON line.
+is N times larger (weak scaling).  Rank 0 prints ONE JSON line.  The same line
+carries, under "extra":
+  cfg1      the fp32 N=3136 configuration (second shape of the metric), 1 GPU only;
+  strong    N>1: the FIXED default batch split into contiguous (batch, head) ranges, 32/N units per rank;
+  seqshard  N>1: one long sequence (B1 H8 N131072) sharded along N: halo exchange + two all-reduces.
 
-`--impl reference` times the CPU restatement of the reference's forward (the
-oracle port, all host threads) on a bounded sample of the same workload.
+`--impl reference` times the reference's CPU forward on a bounded sample of the
+same workload: the reference module itself where its source tree can be
+imported (with the restated window functions), else the oracle port of it.
+`--workload t2t_vit_t14_b64` times the whole T2T-ViT-t-14 forward (batch 64)
+and its two attention stages alone.
 """
 import argparse
 import json
-import math
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -34,8 +41,13 @@ WORKLOADS = {
     'sblocal_bf16_B1_H8_N131072_d128_w512_m512': ('bf16', 1, 8, 131072, 128, 512, 512, 3),
     # a quarter of the default batch: small enough for a multi-pass ncu capture
     'sblocal_bf16_B2_H4_N16384_d64_w256_m256': ('bf16', 2, 4, 16384, 64, 256, 256, 2),
+    # the long sequence of the sharded configuration at the head shape the tensor-core kernels are built for
+    'sblocal_bf16_B1_H8_N131072_d64_w256_m256': ('bf16', 1, 8, 131072, 64, 256, 256, 3),
 }
 DEFAULT_WORKLOAD = 'sblocal_bf16_B2_H16_N16384_d64_w256_m256'
+CFG1_WORKLOAD = 'sblocal_fp32_B8_H1_N3136_d64_w256_m256'
+SEQSHARD_WORKLOAD = 'sblocal_bf16_B1_H8_N131072_d64_w256_m256'
+T2T_WORKLOAD = 't2t_vit_t14_b64'
 METRIC = 'sblocal_attn_fwd_tokens_per_s'
 
 
@@ -47,6 +59,19 @@ def load_peaks():
         return dict(hbm_gbs=pk['hbm_gbs'], bf16_tflops=pk['bf16_tflops'],
                     bf16_tflops_sustained=pk.get('bf16_tflops_sustained'), source='measured')
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source='fallback')
+
+
+def load_band_traffic(B, H, N, d, w, m):
+    """DRAM bytes of one band-kernel launch, from the ncu capture recorded in profiles/band_kernel_dram.json
+    (a smaller batch of the same shape), scaled by the (batch x head) count: traffic grows in proportion to it."""
+    path = os.path.join(ROOT, 'profiles', 'band_kernel_dram.json')
+    if not os.path.exists(path):
+        return None
+    with open(path) as fh:
+        rec = json.load(fh)
+    if (rec['N'], rec['d'], rec['w'], rec['m']) != (N, d, w, m):
+        return None
+    return rec['dram_bytes_per_launch'] * (B * H) / rec['units']
 
 
 def flops_per_token_head(d, D, w, m):
@@ -130,36 +155,234 @@ class ClockSampler:
                     samples=len(sm))
 
 
-def run_reference(args, spec, rank, world):
-    """CPU arm: the oracle port of the reference forward, fp32, all host
-    threads, on a bounded sample (a few (batch, head) units at full N)."""
-    if rank != 0:
-        return
+def time_cpu_forward(spec, units, warmup, steps):
+    """Times the reference's CPU forward on `units` (batch, head) units at full N, fp32, all host threads.
+    Returns (seconds per forward, kind, output of the last forward, its inputs)."""
+    from oracle import ref_bridge
     from oracle import sblocal_oracle as so
     dtype, B, H, N, d, w, m, seed = spec
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    units = max(1, min(B * H, args.cpu_units))
+    torch.set_num_threads(os.cpu_count() or 1)
     q, k, v, W = make_inputs((dtype, units, 1, N, d, w, m, seed), 'cpu')
     q, k, v = q.float(), k.float(), v.float()
-    times = []
-    for i in range(args.warmup_cpu + args.steps_cpu):
-        t0 = time.perf_counter()
-        with torch.no_grad():
-            so.sblocal_forward(q, k, v, W, w, row_chunk=1024)
-        if i >= args.warmup_cpu:
-            times.append(time.perf_counter() - t0)
-    t = sum(times) / len(times)
-    # tokens/s of the full workload = token-heads/s divided by H
-    value = units * N / t / H
+    if ref_bridge.reference_available():
+        kind = 'reference'
+        run = lambda: ref_bridge.reference_forward(q, k, v, W, w)[0]
+    else:
+        kind = 'port'
+        run = lambda: so.sblocal_forward(q, k, v, W, w, row_chunk=1024)[0]
+    times, out = [], None
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            out = run()
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    return sum(times) / len(times), kind, out, (q, k, v, W)
+
+
+def cpu_sample_text(units, spec, kind):
+    dtype, B, H, N = spec[:4]
+    what = ('the reference module (window functions restated on CPU)' if kind == 'reference'
+            else 'the oracle port of the reference forward (the reference tree is not on this machine)')
+    return f'{units} of {B * H} (batch,head) units at full N={N}, fp32, {what}, scaled to whole-batch tokens/s'
+
+
+def run_reference(args, spec, rank):
+    """CPU arm, rank 0 only: a bounded sample of the workload on the host cores."""
+    if rank != 0:
+        return
+    dtype, B, H, N, d, w, m, seed = spec
+    cores = os.cpu_count() or 1
+    units = max(1, min(B * H, args.cpu_units))
+    t, kind, _, _ = time_cpu_forward(spec, units, args.warmup_cpu, args.steps_cpu)
+    value = units * N / t / H          # tokens/s of the full workload = token-heads/s divided by H
     line = dict(metric=METRIC, value=value, unit='tokens/s', impl='reference', n_gpus=args.gpus,
                 steps=args.steps_cpu, warmup=args.warmup_cpu, ms_per_step=t * 1e3, higher_is_better=True,
                 scaling='weak', vs_baseline=None, dtype='f32', data='synthetic',
-                config=dict(workload=args.workload, B=B, H=H, N=N, d=d, window=w, features=m),
-                cpu_baseline=dict(value=value, unit='tokens/s', cores=cores, kind='port',
-                                  sample=f'{units} of {B * H} (batch,head) units at full N={N}, fp32, '
-                                         f'scaled to whole-batch tokens/s'),
+                config=dict(workload=args.workload, B_per_gpu=B, global_batch=B, H=H, N=N, d=d, window=w,
+                            features=m),
+                cpu_baseline=dict(value=value, unit='tokens/s', cores=cores, kind=kind,
+                                  sample=cpu_sample_text(units, spec, kind)),
                 e2e=dict(value=value, unit='tokens/s', h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def timed_blocks(run_step, steps, reps, barrier, flush=None):
+    """`reps` timed blocks of `steps` steps each, every block bracketed by barrier + synchronize; CUDA events
+    on the current stream.  Returns the per-block milliseconds."""
+    out = []
+    for _ in range(reps):
+        barrier()
+        if flush is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                run_step()
+            e1.record()
+            barrier()
+            out.append(e0.elapsed_time(e1))
+        else:
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                     for _ in range(steps)]
+            for a_, b_ in pairs:
+                flush.zero_()
+                a_.record()
+                run_step()
+                b_.record()
+            barrier()
+            out.append(sum(a_.elapsed_time(b_) for a_, b_ in pairs))
+    return out
+
+
+def max_over_ranks(values, dev, world):
+    import torch.distributed as dist
+    t = torch.tensor(values, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t.tolist()]
+
+
+def extra_cfg1(dev, steps):
+    """The fp32 N = 3136 shape of the metric (generic fp32-math kernels), L2 flushed between steps."""
+    from fly_b200 import ops
+    spec = WORKLOADS[CFG1_WORKLOAD]
+    dtype, B, H, N, d, w, m, seed = spec
+    q, k, v, W = (t.to(dev) for t in make_inputs(spec, 'cpu'))
+    prob = ops.Problem(q, k, v, W, w)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        prob.forward()
+    ms = timed_blocks(prob.forward, steps, 3, lambda: torch.cuda.synchronize(dev), flush)
+    ms_step = statistics.median(ms) / steps
+    flops = flops_per_token_head(d, d, w, m) * B * H * N
+    return dict(workload=CFG1_WORKLOAD, dtype='f32', ms_per_step=ms_step, tokens_per_s=B * N / (ms_step * 1e-3),
+                tflops=flops / (ms_step * 1e-3) / 1e12, kernels='generic SIMT fp32 math',
+                l2='256 MB buffer rewritten between timed steps')
+
+
+def extra_strong(dev, rank, world, spec, steps, barrier):
+    """Strong scaling of the default batch: its B*H (batch, head) units are split into `world` contiguous
+    ranges, one per rank, no collective; tokens/s = B*N / (slowest rank's time per forward)."""
+    from fly_b200 import ops
+    dtype, B, H, N, d, w, m, seed = spec
+    units = B * H
+    if units % world != 0:
+        return dict(skipped=f'{units} units do not split evenly over {world} ranks')
+    per = units // world
+    u0 = rank * per
+    b0, h0 = divmod(u0, H)
+    q, k, v, W = make_inputs(spec, 'cpu')
+    if per >= H:                      # whole batches per rank
+        nb = per // H
+        sl = lambda t: t[b0:b0 + nb]
+    else:                             # a range of heads of one batch entry (strided views, passed as strides)
+        sl = lambda t: t[b0:b0 + 1, :, h0:h0 + per]
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    prob = ops.Problem(sl(qd), sl(kd), sl(vd), W.to(dev), w)
+    for _ in range(5):
+        prob.forward()
+    ms = timed_blocks(prob.forward, steps, 5, barrier)
+    ms = max_over_ranks(ms, dev, world)
+    prob.check_status()
+    ms_step = statistics.median(ms) / steps
+    return dict(workload=DEFAULT_WORKLOAD, units_per_rank=per, ms_per_step=ms_step,
+                tokens_per_s=B * N / (ms_step * 1e-3), scaling='strong',
+                note='fixed global batch; inputs of a rank (%.0f MB) %s the 126 MB L2'
+                     % (4 * per * N * d * 2 / 1e6, 'exceed' if 4 * per * N * d * 2 > 126e6 else 'fit in'))
+
+
+def extra_seqshard(dev, rank, world, steps, barrier):
+    """One long sequence sharded along N over the ranks: halo exchange (point to point), MAX all-reduce of the
+    key log-scale, SUM all-reduce of [KV | sum phi(K)], then the band stage on local memory."""
+    import torch.distributed as dist
+    from fly_b200 import ops
+    from fly_b200.seqshard import sblocal_forward_seqshard, shard_bounds
+    spec = WORKLOADS[SEQSHARD_WORKLOAD]
+    dtype, B, H, N, d, w, m, seed = spec
+    q, k, v, W = make_inputs(spec, 'cpu')
+    bounds = shard_bounds(N, world)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    ql, kl, vl, Wd = q[:, lo:hi].to(dev), k[:, lo:hi].to(dev), v[:, lo:hi].to(dev), W.to(dev)
+    run = lambda timings=None: sblocal_forward_seqshard(ql, kl, vl, Wd, w, N, timings=timings)
+    for _ in range(3):
+        out = run()
+    ms = timed_blocks(run, steps, 3, barrier)
+    stages = []
+    run(stages)
+    torch.cuda.synchronize(dev)
+    stage_ms = {name: stages[i - 1][1].elapsed_time(ev) for i, (name, ev) in enumerate(stages) if i > 0}
+    vals = max_over_ranks(ms + [stage_ms['halo+max'], stage_ms['allreduce'], stage_ms['band'],
+                                stage_ms['logscale'], stage_ms['summary']], dev, world)
+    ms_step = statistics.median(vals[:3]) / steps
+    # parity of the sharded result against the same sequence run on one GPU (rank 0 holds both)
+    gathered = [torch.empty(B, bounds[r + 1] - bounds[r], H, d, device=dev, dtype=out.dtype) for r in range(world)]
+    dist.all_gather(gathered, out.contiguous())
+    rel = None
+    if rank == 0:
+        single = ops.Problem(q.to(dev), k.to(dev), v.to(dev), Wd, w)
+        ref = single.forward().float()
+        single.check_status()
+        got = torch.cat(gathered, dim=1).float()
+        rel = float((got - ref).abs().max() / ref.abs().max())
+    halo_ms, ar_ms, band_ms, ls_ms, sum_ms = vals[3:]
+    return dict(workload=SEQSHARD_WORKLOAD, ms_per_step=ms_step, tokens_per_s=B * N / (ms_step * 1e-3),
+                rel_err_vs_single_gpu=rel, halo_ms=halo_ms, allreduce_ms=ar_ms,
+                stage_ms=dict(logscale=ls_ms, halo_and_max_allreduce=halo_ms, summary=sum_ms, sum_allreduce=ar_ms,
+                              band=band_ms),
+                not_overlapped='the SUM all-reduce (every band tile needs the reduced summary) and what is left of '
+                               'the halo wait after the key log-scale pass, which runs while the halo rows fly',
+                note='config 5 sequence length at the d=64/w=256/m=256 head shape of the tensor-core kernels')
+
+
+def run_t2t(args, dev):
+    """Whole T2T-ViT-t-14 forward (random-init, fp32 images) with SBLocal attention in both token stages, and the
+    two attention stages alone; inputs come from pinned host memory and logits return to the host every step."""
+    from fly_b200 import ops, t2t_vit
+    batch = 64
+    torch.manual_seed(0)
+    model = t2t_vit.t2t_vit_t_14(t2t_vit.sblocal_factory(256, 256), t2t_vit.sblocal_factory(256, 256)).eval()
+    layers = [model.patch_embed.attention1.attn.attention_layer, model.patch_embed.attention2.attn.attention_layer]
+    for layer in layers:
+        layer.feature_map.new_feature_map('cpu')
+    model = model.to(dev)
+    img_h = torch.randn(batch, 3, 224, 224).pin_memory()
+    logits_h = torch.empty(batch, 1000).pin_memory()
+
+    def step():
+        with torch.no_grad():
+            logits_h.copy_(model(img_h.to(dev, non_blocking=True)), non_blocking=True)
+
+    out = {}
+    for name, cdt in (('fp32_attention', None), ('bf16_attention', torch.bfloat16)):
+        for layer in layers:
+            layer.compute_dtype = cdt
+        for _ in range(max(3, args.warmup)):
+            step()
+        ms = timed_blocks(step, args.steps, 3, lambda: torch.cuda.synchronize(dev))
+        whole = statistics.median(ms) / args.steps
+        # the two attention calls alone, on inputs of the shapes and temperatures the model feeds them
+        attn_ms = 0.0
+        for N, tau in ((3136, 147 ** -0.5), (784, 576 ** -0.5)):
+            g = torch.Generator().manual_seed(N)
+            q, k, v = ((torch.randn(batch, N, 1, 64, generator=g) / 64 ** 0.25).to(dev) for _ in range(3))
+            if cdt is not None:
+                q, k, v = q.to(cdt), k.to(cdt), v.to(cdt)
+            prob = ops.Problem(q, k, v, layers[0].feature_map.projection_matrix, 256, tau)
+            for _ in range(3):
+                prob.forward()
+            a_ms = timed_blocks(prob.forward, args.steps, 3, lambda: torch.cuda.synchronize(dev))
+            attn_ms += statistics.median(a_ms) / args.steps
+        out[name] = dict(ms_per_step=whole, images_per_s=batch / (whole * 1e-3), attention_only_ms=attn_ms)
+    line = dict(metric='t2t_vit_t14_fwd_images_per_s', value=out['fp32_attention']['images_per_s'], unit='images/s',
+                n_gpus=1, steps=args.steps, warmup=max(3, args.warmup),
+                ms_per_step=out['fp32_attention']['ms_per_step'], higher_is_better=True, scaling='weak',
+                vs_baseline=None, dtype='f32', data='synthetic',
+                config=dict(workload=T2T_WORKLOAD, batch=batch, image='3x224x224 fp32 N(0,1)', weights='random init',
+                            attention='SBLocal w=256 m=256 in both T2T stages (N=3136, N=784, d=64)',
+                            backbone='14 dense blocks, width 384, torch scaled_dot_product_attention'),
+                e2e=dict(value=out['fp32_attention']['images_per_s'], unit='images/s',
+                         h2d_bytes_per_step=img_h.numel() * 4, d2h_bytes_per_step=logits_h.numel() * 4),
+                variants=out)
     print(json.dumps(line))
 
 
@@ -168,22 +391,24 @@ def main():
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=50)
     ap.add_argument('--warmup', type=int, default=5)
-    ap.add_argument('--workload', default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument('--reps', type=int, default=5, help='timed blocks of --steps steps; the median block is reported')
+    ap.add_argument('--workload', default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [T2T_WORKLOAD])
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--cpu-units', type=int, default=2, help='(batch,head) units in the CPU sample')
+    ap.add_argument('--cpu-units', type=int, default=4, help='(batch,head) units in the CPU sample')
     ap.add_argument('--steps-cpu', type=int, default=2)
     ap.add_argument('--warmup-cpu', type=int, default=1)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-extras', action='store_true', help='skip the cfg1 / strong / seqshard side measurements')
     ap.add_argument('--profile', action='store_true',
                     help='run only warm-up and the timed forwards (for ncu captures); prints no JSON line')
     args = ap.parse_args()
-    spec = WORKLOADS[args.workload]
     rank = int(os.environ.get('RANK', '0'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
 
     if args.impl == 'reference':
-        run_reference(args, spec, rank, world)
+        spec = WORKLOADS[DEFAULT_WORKLOAD if args.workload == T2T_WORKLOAD else args.workload]
+        run_reference(args, spec, rank)
         return
 
     if not torch.cuda.is_available():
@@ -194,9 +419,16 @@ def main():
     _cabi.load()
     torch.cuda.set_device(local_rank)
     dev = torch.device('cuda', local_rank)
+    if args.workload == T2T_WORKLOAD:
+        if rank == 0:
+            run_t2t(args, dev)
+        return
     if world > 1:
+        # the collectives of the side measurements are small and latency-bound; keep them on plain rings
+        os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
         dist.init_process_group('nccl', device_id=dev)
     args.warmup = max(args.warmup, 3)
+    spec = WORKLOADS[args.workload]
 
     dtype, B, H, N, d, w, m, seed = spec
     q_h, k_h, v_h, W = make_inputs(spec, 'cpu', seed_offset=rank)
@@ -204,7 +436,7 @@ def main():
     q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     Wd = W.to(dev)
     prob = ops.Problem(q, k, v, Wd, w)
-    tensor_path = bool(_cabi.load().sbl_has_tensor_path()) and dtype == 'bf16'
+    tensor_path = prob.status_offset is not None
 
     def barrier():
         if world > 1:
@@ -223,24 +455,8 @@ def main():
     barrier()
     if rank == 0:
         sampler.start()
-    if flush is None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            prob.forward()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-    else:
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                 for _ in range(args.steps)]
-        for a_, b_ in pairs:
-            flush.zero_()
-            a_.record()
-            prob.forward()
-            b_.record()
-        barrier()
-        ms = sum(a_.elapsed_time(b_) for a_, b_ in pairs)
+    reps = 1 if args.profile else max(1, args.reps)
+    block_ms = timed_blocks(prob.forward, args.steps, reps, barrier, flush)
     if rank == 0 and not args.profile:
         # nvidia-smi cannot sample faster than the timed region is long (tens of milliseconds): keep the same
         # step running for 0.6 s more (untimed, results discarded) so that the samples show the clocks under
@@ -252,10 +468,10 @@ def main():
             torch.cuda.synchronize(dev)
     clocks = sampler.stop() if rank == 0 else None
     if clocks is not None:
-        clocks['sampled_over'] = 'timed region + 0.6 s untimed repeat of the same step, nvidia-smi every 50 ms'
+        clocks['sampled_over'] = 'timed blocks + 0.6 s untimed repeat of the same step, nvidia-smi every 50 ms'
     if args.profile:
         prob.check_status()
-        print(f'profile run: {ms / args.steps:.4f} ms per forward (not a benchmark value)')
+        print(f'profile run: {block_ms[0] / args.steps:.4f} ms per forward (not a benchmark value)')
         return
 
     # ---- per-stage timing on the launch stream (roofline of the band kernel) ----
@@ -333,11 +549,21 @@ def main():
         e2e_reps.append(s0.elapsed_time(s1))
     e2e_ms = sorted(e2e_reps)[1]
 
-    t = torch.tensor([ms, e2e_ms, band_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, band_ms = (float(x) for x in t.tolist())
+    vals = max_over_ranks(block_ms + [e2e_ms, band_ms], dev, world)
+    block_ms, e2e_ms, band_ms = vals[:reps], vals[reps], vals[reps + 1]
     prob.check_status()     # raises if any kernel gave up on a bounded wait
+    ms = statistics.median(block_ms)
+
+    # ---- side measurements (all ranks take part in the distributed ones) ----
+    extra = {}
+    if not args.no_extras and args.workload == DEFAULT_WORKLOAD:
+        side_steps = max(3, min(args.steps, 10))
+        if world == 1:
+            if rank == 0:
+                extra['cfg1'] = extra_cfg1(dev, side_steps)
+        else:
+            extra['strong'] = extra_strong(dev, rank, world, spec, side_steps, barrier)
+            extra['seqshard'] = extra_seqshard(dev, rank, world, side_steps, barrier)
 
     if rank == 0:
         peaks = load_peaks()
@@ -352,9 +578,7 @@ def main():
         peak_tf = peaks['bf16_tflops']
         achieved = band_flops / (band_ms * 1e-3) / 1e12
         launches_per_step = 5 if tensor_path else 8
-        # dram__bytes_read.sum + dram__bytes_write.sum of one tc_band_kernel launch, from the ncu capture summarised
-        # in profiles/tc_band_kernel_B2_H4_N16384.md (quarter batch: 159.4 MB), scaled by the (batch x head) count
-        band_traffic = (159.4e6 * (B * H) / 8.0) if (tensor_path and N == 16384) else None
+        band_traffic = load_band_traffic(B, H, N, d, w, m) if tensor_path else None
         line = dict(
             metric=METRIC, value=value, unit='tokens/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=ms_per_step, higher_is_better=True, scaling='weak', vs_baseline=None,
@@ -366,6 +590,8 @@ def main():
                             'L2 flushed (256 MB buffer rewritten) between timed steps; inputs of one step are %.0f MB'
                             % (4 * th * d * elem / 1e6)),
                         kernels='tcgen05+TMA bf16' if tensor_path else 'generic SIMT fp32 math'),
+            timed_blocks=dict(count=reps, steps_each=args.steps, ms_per_step_median=ms_per_step,
+                              ms_per_step_min=min(block_ms) / args.steps, ms_per_step_max=max(block_ms) / args.steps),
             clocks=clocks,
             e2e=dict(value=e2e_value, unit='tokens/s', h2d_bytes_per_step=3 * th * d * elem,
                      d2h_bytes_per_step=th * d * elem, steps=e2e_steps,
@@ -380,6 +606,8 @@ def main():
                                   hbm_gbs=4 * th * d * elem / (ms_per_step * 1e-3) / 1e9,
                                   hbm_peak_gbs=peaks['hbm_gbs']),
         )
+        if extra:
+            line['extra'] = extra
         if not tensor_path:
             # The generic path computes in fp32 on the FMA pipe: its ceiling is the FP32 peak, not the tensor peak.
             # Measured here with an fp32 (TF32 off) cuBLAS GEMM, 8192^3, best of 5.
@@ -404,18 +632,10 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             from oracle import sblocal_oracle as so
             cores = os.cpu_count() or 1
-            torch.set_num_threads(cores)
             units = max(1, min(B * H, args.cpu_units))
-            cq, ck, cv, cW = make_inputs((dtype, units, 1, N, d, w, m, seed), 'cpu')
-            cq, ck, cv = cq.float(), ck.float(), cv.float()
-            with torch.no_grad():
-                so.sblocal_forward(cq, ck, cv, cW, w, row_chunk=1024)
-                t0 = time.perf_counter()
-                ref_out, _ = so.sblocal_forward(cq, ck, cv, cW, w, row_chunk=1024)
-                cpu_t = time.perf_counter() - t0
-            line['cpu_baseline'] = dict(
-                value=units * N / cpu_t / H, unit='tokens/s', cores=cores, kind='port',
-                sample=f'{units} of {B * H} (batch,head) units at full N={N}, fp32, scaled to whole-batch tokens/s')
+            cpu_t, kind, ref_out, (cq, ck, cv, cW) = time_cpu_forward(spec, units, 1, 1)
+            line['cpu_baseline'] = dict(value=units * N / cpu_t / H, unit='tokens/s', cores=cores, kind=kind,
+                                        sample=cpu_sample_text(units, spec, kind))
             # the same sample through the CUDA path, as a live parity figure
             dq, dk, dv = (x.to(dev).to(q.dtype) for x in (cq, ck, cv))
             got = ops.sblocal_forward(dq, dk, dv, cW.to(dev), w).float().cpu()

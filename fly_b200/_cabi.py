@@ -26,7 +26,7 @@ ABI_VERSION = 1
 EXPORTS = ('sbl_version', 'sbl_last_error', 'sbl_has_tensor_path', 'sbl_workspace_bytes', 'sbl_forward',
            'sbl_key_logscale', 'sbl_key_summary', 'sbl_band_forward', 'sbl_query_features',
            'sbl_key_features', 'sbl_attention_weights', 'sbl_check_status', 'sbl_selftest_wait_timeout',
-           'sbl_key_logscale_static', 'sbl_static_last_error')
+           'sbl_key_logscale_static', 'sbl_static_last_error', 'sbl_status_words')
 
 
 class SblParams(ctypes.Structure):
@@ -113,6 +113,8 @@ def load():
         lib.sbl_attention_weights.argtypes = [P, vp, sz, vp, vp, vp, vp]
         lib.sbl_check_status.restype = ctypes.c_int
         lib.sbl_check_status.argtypes = [P, vp, sz, vp]
+        lib.sbl_status_words.restype = ctypes.c_int
+        lib.sbl_status_words.argtypes = [P, ctypes.POINTER(sz)]
         lib.sbl_selftest_wait_timeout.restype = ctypes.c_int
         lib.sbl_selftest_wait_timeout.argtypes = [vp, sz, vp]
         lib.sbl_key_logscale_static.restype = ctypes.c_int

@@ -72,8 +72,9 @@ def build(force=False, verbose=False):
             print(out)
         if pr.returncode != 0:
             raise RuntimeError(f'nvcc failed on {src}')
+    # no -lcuda: the one driver entry point the library needs is looked up at run time (sbl_tmap.cu)
     link = [_nvcc(), '-shared', '-gencode', 'arch=compute_100a,code=sm_100a', '-o', LIB_PATH, *objs,
-            '-lcuda', '-cudart', 'static']
+            '-cudart', 'static']
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         print(res.stdout)

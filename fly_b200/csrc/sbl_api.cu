@@ -77,22 +77,13 @@ int check_workspace(const Workspace& ws, void* workspace, size_t bytes) {
 int prepare(const SblParams* p, void* workspace, size_t bytes, Workspace* ws) {
   int rc = validate(p);
   if (rc != SBL_OK) return rc;
-  const char* why = "";
-  if (!plan_workspace(*p, ws, &why)) return fail(SBL_ERR_INVALID_ARGUMENT, "%s", why);
+  plan_workspace(*p, ws);
   return check_workspace(*ws, workspace, bytes);
-}
-
-// Tensor-path kernels record a ran-out wait in the workspace status word; it
-// is read (with a stream synchronisation) only by sbl_check_status, so the
-// forward itself never blocks the host.
-int check_device_status(const Workspace& ws, char* base, cudaStream_t st) {
-  (void)ws; (void)base; (void)st;
-  return SBL_OK;
 }
 
 }  // namespace
 
-bool plan_workspace(const SblParams& p, Workspace* ws, const char** why) {
+void plan_workspace(const SblParams& p, Workspace* ws) {
   const size_t BH = (size_t)p.B * p.H, m = 2 * (size_t)p.r;
   ws->tensor = tc_supported(p) && !(p.flags & SBL_FLAG_GENERIC_PATH);
   // split the summary over key rows: at most 64 splits, at least 256 rows each
@@ -122,8 +113,6 @@ bool plan_workspace(const SblParams& p, Workspace* ws, const char** why) {
   ws->lognorm = off; off = align_up(off + (ws->tensor ? 0 : BH * p.T * 4));
   ws->status = off;  off = align_up(off + 64);
   ws->total = off;
-  (void)why;
-  return true;
 }
 
 }  // namespace sbl
@@ -152,8 +141,7 @@ int sbl_workspace_bytes(const SblParams* p, size_t* bytes) {
   int rc = validate(p);
   if (rc != SBL_OK) return rc;
   Workspace ws;
-  const char* why = "";
-  if (!plan_workspace(*p, &ws, &why)) return fail(SBL_ERR_INVALID_ARGUMENT, "%s", why);
+  plan_workspace(*p, &ws);
   *bytes = ws.total;
   return SBL_OK;
 }
@@ -188,7 +176,7 @@ int sbl_key_summary(const SblParams* p, void* workspace, size_t workspace_bytes,
   if (ws.tensor) {
     if ((e = tc_prepare_projection(*p, ws, base, st, false)) != cudaSuccess) return cuda_fail(e, "prepare projection");
     if ((e = tc_key_summary(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "key summary");
-    return check_device_status(ws, base, st);
+    return SBL_OK;
   }
   float* phik = reinterpret_cast<float*>(base + ws.phik);
   if ((e = f32_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
@@ -209,7 +197,7 @@ int sbl_band_forward(const SblParams* p, void* workspace, size_t workspace_bytes
   if (ws.tensor) {
     if ((e = tc_prepare_projection(*p, ws, base, st, false)) != cudaSuccess) return cuda_fail(e, "prepare projection");
     if ((e = tc_band(*p, ws, base, beta, kv, ksum, st)) != cudaSuccess) return cuda_fail(e, "band forward");
-    return check_device_status(ws, base, st);
+    return SBL_OK;
   }
   if ((e = f32_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
   if ((e = f32_query_features(*p, ws, base, reinterpret_cast<float*>(base + ws.phiq),
@@ -237,7 +225,7 @@ int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, voi
       return cuda_fail(e, "key logscale bound");
     if ((e = tc_key_summary(*p, ws, base, beta, kv, ksum, st, true)) != cudaSuccess) return cuda_fail(e, "key summary");
     if ((e = tc_band(*p, ws, base, beta, kv, ksum, st, true)) != cudaSuccess) return cuda_fail(e, "band forward");
-    return check_device_status(ws, base, st);
+    return SBL_OK;
   }
   float* phik = reinterpret_cast<float*>(base + ws.phik);
   if ((e = f32_prepare_projection(*p, ws, base, st)) != cudaSuccess) return cuda_fail(e, "prepare projection");
@@ -277,12 +265,27 @@ int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes
     cudaError_t e = cudaStreamSynchronize(st);
     return e == cudaSuccess ? SBL_OK : cuda_fail(e, "stream synchronize");
   }
-  int host = 0;
-  cudaError_t e = tc_read_status(ws, static_cast<char*>(workspace), &host, st);
+  int host[2] = {0, 0};
+  cudaError_t e = tc_read_status(ws, static_cast<char*>(workspace), host, st);
   if (e != cudaSuccess) return cuda_fail(e, "read device status");
-  if (host != 0)
+  if (host[0] != 0)
     return fail(SBL_ERR_DEVICE_STATUS, "a bounded wait ran out inside a kernel (wait site %d); results are invalid",
-                host);
+                host[0]);
+  if (host[1] != 0)
+    return fail(SBL_ERR_DEVICE_STATUS,
+                "numeric range: an exponential of the bf16 tensor-core kernels left the fp32 range (logits far above "
+                "unit scale); results are invalid -- rerun with SBL_FLAG_GENERIC_PATH");
+  return SBL_OK;
+}
+
+int sbl_status_words(const SblParams* p, size_t* offset) {
+  if (!offset) return fail(SBL_ERR_INVALID_ARGUMENT, "offset is null");
+  int rc = validate(p);
+  if (rc != SBL_OK) return rc;
+  Workspace ws;
+  plan_workspace(*p, &ws);
+  if (!ws.tensor) return fail(SBL_ERR_UNSUPPORTED, "the generic kernels keep no status words");
+  *offset = ws.status;
   return SBL_OK;
 }
 

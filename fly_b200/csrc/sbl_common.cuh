@@ -31,9 +31,8 @@ struct Workspace {
   bool tensor;      // true: tcgen05/TMA bf16 kernels are used
 };
 
-// Fills the layout for a problem; returns false (with a message) when the
-// problem is malformed.
-bool plan_workspace(const SblParams& p, Workspace* ws, const char** why);
+// Fills the layout for a problem.
+void plan_workspace(const SblParams& p, Workspace* ws);
 
 inline __host__ __device__ int64_t div_up(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
@@ -71,7 +70,8 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
                     const float* kv, const float* ksum, cudaStream_t st, bool kv16_ready = false);
 // runs a kernel whose only wait can never be satisfied; *host_status receives the recorded wait site (99)
 cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t st);
-// copies the device status word to *host_status and synchronises the stream
+// copies the two device status words (host_status[0]: wait site that ran out, host_status[1]: 1 if an
+// exponential left the fp32 range) and synchronises the stream
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st);
 
 }  // namespace sbl

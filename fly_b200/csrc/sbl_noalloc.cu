@@ -21,7 +21,18 @@
 //     on the GPU (different streams) race on it: serialise them.
 //   * the first call on each device looks up the array's device address.
 //     That lookup is a CUDA runtime call, so make this first call during
-//     start-up, ahead of any stream capture.
+//     start-up, ahead of any stream capture.  The first launch of a kernel
+//     in a process may also load its code: make one start-up call per input
+//     dtype you will use (fp32 and bf16 keys run different instantiations).
+//     The address is remembered per device for the life of the process; a
+//     cudaDeviceReset invalidates it, so do not reset a device and go on
+//     using this entry point.
+//   * the value is the exact key log-scale computed with the fp32 projection
+//     by the generic kernels: equal to sbl_key_logscale with
+//     SBL_FLAG_GENERIC_PATH.  For bf16 inputs of the tensor-core shape
+//     (E = 64, r = 128) the plain sbl_key_logscale rounds the projection to
+//     bf16 first, so the two differ there by up to a few 1e-2 (either is a
+//     valid stabiliser).
 //   * neither this function nor anything it calls allocates or frees memory.
 #include <cstdio>
 #include <mutex>
@@ -81,6 +92,11 @@ int sbl_key_logscale_static(const SblParams* p, float* beta, void* cuda_stream) 
   if (!p->k || !p->W) return reject(SBL_ERR_INVALID_ARGUMENT, "k and W must be non-null device pointers");
   if (p->sum_lo < 0 || p->sum_hi > p->S || p->sum_lo > p->sum_hi)
     return reject(SBL_ERR_INVALID_ARGUMENT, "summary rows must lie inside the key buffer");
+  if (p->k_stride_b < 0 || p->k_stride_s < p->E || p->k_stride_h < 0)
+    return reject(SBL_ERR_INVALID_ARGUMENT, "key strides must be non-negative element strides, rows at least E apart");
+  for (int i = 0; i < 3; ++i)
+    if (p->reserved[i] != 0) return reject(SBL_ERR_INVALID_ARGUMENT, "reserved fields must be 0");
+  if (p->flags & ~SBL_FLAG_GENERIC_PATH) return reject(SBL_ERR_INVALID_ARGUMENT, "unknown flag bits");
   if ((int64_t)p->r * p->E > kStaticProjFloats) {
     snprintf(g_msg, sizeof(g_msg),
              "r*E = %lld floats exceeds the built-in scratch of %d floats; use sbl_key_logscale with a workspace",

@@ -1,8 +1,8 @@
 // bf16 tensor-core path of the SBLocal forward for sm_100a: TMA tile loads,
-// tcgen05.mma with accumulators (and the phi(Q) / weight operands) in tensor
-// memory, warp-specialised pipelines with mbarriers whose waits are bounded.
-// Shapes: E = D = 64, r = 128 (m = 256), eps = 0, any T, S, w, key lengths.
-// Everything else takes the generic kernels of sbl_f32.cu.
+// tcgen05.mma with accumulators (and the phi(Q) / packed-weight operands) in
+// tensor memory, warp-specialised pipelines with mbarriers whose waits are
+// bounded.  Shapes: E = D = 64, r = 128 (m = 256), eps = 0, any T, S, w, key
+// lengths.  Everything else takes the generic kernels of sbl_f32.cu.
 //
 // Kernels
 //   prep      sqrt(tau)*W -> bf16 (and fp32), clears the status words (and, for the fused forward, the log-scales)
@@ -13,18 +13,33 @@
 //             memory for KV += phi(K)^T [V | 1] (accumulators in tensor memory),
 //             then one partial summary per CTA
 //   combine   sums the split partials -> KV (fp32, and bf16 for the band kernel), sum phi(K)
-//   band      persistent, one CTA per SM walking a run of 128-query tiles: U = Q Wt^T ->
-//             phi(Q) packed bf16 into tensor memory (the A operand of every phi(Q)
-//             product); O = phi(Q) KV; then per 128-key tile S = Q K^T into one of
-//             two tensor-memory buffers, the softmax warps write
-//             E = exp(tau S - pls) (masked to the window and key length) back over
-//             S in fp32, the tensor core subtracts P = phi(Q) phi(K)^T from it (same
-//             MMA, A operand negated), the softmax warps pack D = E - P to bf16,
-//             O += D V; finally out = O / max(Z + sum D, L + 1e-24), staged in shared
-//             memory and written by one bulk tensor store per tile.
+//   band      persistent, one CTA per SM walking a run of 128-query tiles.  The
+//             projection U = Q Wt^T is computed in two halves of 64 projections,
+//             each into a 64-column slot of tensor memory, where the softmax
+//             warps turn it IN PLACE into 128 bf16 features (the A operand of
+//             every phi(Q) product); three such slots rotate, so the features of
+//             the next query tile are formed while the current tile still uses
+//             its own.  Per 128-key tile: S = Q K^T into one of two buffers, the
+//             softmax warps write E = exp(tau S - pls) (masked to the window and
+//             key length) back over S in fp32, the tensor core subtracts
+//             P = phi(Q) phi(K)^T from it (same MMA, A operand negated, one
+//             product per feature half), the softmax warps pack D = E - P to
+//             bf16 over the first half of their own columns, O += D V;
+//             O also receives phi(Q) KV; finally out = O / max(Z + sum D, L + 1e-24),
+//             staged in shared memory and written by one bulk tensor store per tile.
 //   Everything is kept in "feature units" (divided by e^{pls}, pls = query
 //   log-scale + beta), so the exact and the low-rank terms share one
 //   accumulator and no accumulator is ever rescaled.
+//
+// Feature order.  Inside this path the 256 features are ordered so that the
+// 32 features a softmax thread forms from its 16 projections sit in the 16
+// tensor-memory columns it read those projections from: slot
+// kp = 128*h + 32*c + 16*s + j holds feature exp((-1)^s u_p ...) of projection
+// p = 64*h + 16*c + j (reference index p + 128*s).  phi(K) in the workspace, the
+// split partials and the bf16 KV use this order; the fp32 kv / ksum the API
+// exchanges with callers use the reference's.
+#include <mutex>
+
 #include "sbl_common.cuh"
 #include "sbl_tc_ptx.cuh"
 
@@ -200,34 +215,48 @@ __global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* 
   }
 }
 
-// kv (BH,256,64), ksum (BH,256) = sum over the splits of the per-CTA partial summaries
+// Reference feature index of internal slot kp (see "Feature order" at the top of the file).
+__host__ __device__ constexpr int feat_of_slot(int kp) {
+  return 64 * (kp >> 7) + 16 * ((kp >> 5) & 3) + (kp & 15) + 128 * ((kp >> 4) & 1);
+}
+
+// kv (BH,256,64), ksum (BH,256) = sum over the splits of the per-CTA partial summaries.  The partials and
+// kv16 (the band kernel's bf16 operand) are in the internal feature order, kv and ksum in the reference's.
 __global__ void tc_combine_kernel(const float* partial, int nsplit, int BH, float* kv, float* ksum,
                                   __nv_bfloat16* kv16) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over BH * 256 * 20 float4 groups
   if (i >= (int64_t)BH * kM * (kPartialLd / 4)) return;
   const int g = (int)(i % (kPartialLd / 4));
-  const int64_t bf = i / (kPartialLd / 4);        // bh * 256 + f
+  const int64_t bf = i / (kPartialLd / 4);        // bh * 256 + slot
   if (g > 16) return;
-  const int64_t bh = bf / kM, f = bf % kM;
+  const int64_t bh = bf / kM;
+  const int kp = (int)(bf % kM);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int k = 0; k < nsplit; ++k) {
-    const float4 v = *reinterpret_cast<const float4*>(partial + ((bh * nsplit + k) * kM + f) * kPartialLd + 4 * g);
+    const float4 v = *reinterpret_cast<const float4*>(partial + ((bh * nsplit + k) * kM + kp) * kPartialLd + 4 * g);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
+  const int64_t out_row = bh * kM + feat_of_slot(kp);
   if (g < 16) {
-    *reinterpret_cast<float4*>(kv + bf * kE + 4 * g) = acc;
+    *reinterpret_cast<float4*>(kv + out_row * kE + 4 * g) = acc;
     if (kv16) {   // the band kernel's bf16 operand, when the caller goes straight on to the band stage
       const uint2 h = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
       *reinterpret_cast<uint2*>(kv16 + bf * kE + 4 * g) = h;
     }
   } else {
-    ksum[bf] = acc.x;
+    ksum[out_row] = acc.x;
   }
 }
 
+// kv (BH,256,64) fp32 in the reference's feature order -> bf16 in the internal order
 __global__ void tc_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64_t n) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) kv16[i] = __float2bfloat16_rn(kv[i]);
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over output elements
+  if (i >= n) return;
+  const int d = (int)(i % kE);
+  const int64_t row = i / kE;
+  const int64_t bh = row / kM;
+  const int kp = (int)(row % kM);
+  kv16[i] = __float2bfloat16_rn(kv[(bh * kM + feat_of_slot(kp)) * kE + d]);
 }
 
 // ---------------------------------------------------------------------------
@@ -238,8 +267,8 @@ struct KeysArgs {
   const int64_t* lengths;
   const float* beta_in;   // !MAX
   float* beta_out;        // MAX
-  __nv_bfloat16* phik;    // (BH, S, 256)
-  float* partial;         // (BH, nsplit, 256, 65)
+  __nv_bfloat16* phik;    // (BH, S, 256), internal feature order
+  float* partial;         // (BH, nsplit, 256, 80)
   int* status;
   int S, H, sum_lo, sum_hi, nsplit;
   int64_t k_pos0, S_total;
@@ -248,7 +277,7 @@ struct KeysArgs {
 
 namespace keys {
 constexpr int TILE = 128;
-constexpr int NFQ = 2;                     // projection groups per key row: a feature thread owns 128/NFQ projections
+constexpr int NFQ = 4;                     // projection groups per key row: a feature thread owns 128/NFQ projections
 constexpr int NFEAT = 128 * NFQ;           // feature threads: warp w owns key rows 32*(w%4).., projection group w/4
 constexpr int CHK = 4 / NFQ;               // 32-projection chunks per thread
 constexpr int WPK = NFEAT / 32;            // producer warp; WPK+1: MMA warp
@@ -499,27 +528,27 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
             p1[j] = live ? pack_bf16(ep.x, ep.y) : 0u;
             p2[j] = live ? pack_bf16(em.x, em.y) : 0u;
           }
+          // A chunk of 32 projections fills one 64-feature block of the internal order: per group of 16
+          // projections (gi) two 16-byte pieces of the "+" features, then two of the "-" features.
+          const int blk = f0 >> 5;
           if (!plain && row < a.S) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              reinterpret_cast<uint4*>(grow + f0)[q] = make_uint4(p1[4 * q], p1[4 * q + 1], p1[4 * q + 2], p1[4 * q + 3]);
-              reinterpret_cast<uint4*>(grow + kR + f0)[q] =
-                  make_uint4(p2[4 * q], p2[4 * q + 1], p2[4 * q + 2], p2[4 * q + 3]);
+            for (int q8 = 0; q8 < 8; ++q8) {
+              const uint32_t* src = ((q8 >> 1) & 1) ? p2 : p1;
+              const int o = 8 * (q8 >> 2) + 4 * (q8 & 1);
+              reinterpret_cast<uint4*>(grow + 64 * blk)[q8] = make_uint4(src[o], src[o + 1], src[o + 2], src[o + 3]);
             }
           }
           // the previous tile's MMAs and bulk store must be done with the shared phi(K) buffer
           if (c == 0 && i >= 2) mbar_wait(a_free + s, ((i >> 1) - 1) & 1, a.status, 17);
-          // MN-major A operand: block = feature / 64, 16-byte chunk = (feature % 64) / 8, swizzled by key % 8
-          const int blk = f0 >> 6;
+          // MN-major A operand: block = 64 features, 16-byte piece q8 of the key's 128-byte line, swizzled by key % 8
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int chunk = ((f0 & 63) >> 3) + q;
-            const uint32_t o = (uint32_t)krow * 128u + (uint32_t)((chunk ^ (krow & 7)) << 4);
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(sA + blk * 16384 + o) =
-                in_sum ? make_uint4(p1[4 * q], p1[4 * q + 1], p1[4 * q + 2], p1[4 * q + 3]) : z;
-            *reinterpret_cast<uint4*>(sA + (2 + blk) * 16384 + o) =
-                in_sum ? make_uint4(p2[4 * q], p2[4 * q + 1], p2[4 * q + 2], p2[4 * q + 3]) : z;
+          for (int q8 = 0; q8 < 8; ++q8) {
+            const uint32_t* src = ((q8 >> 1) & 1) ? p2 : p1;
+            const int o = 8 * (q8 >> 2) + 4 * (q8 & 1);
+            const uint32_t so = (uint32_t)krow * 128u + (uint32_t)((q8 ^ (krow & 7)) << 4);
+            *reinterpret_cast<uint4*>(sA + blk * 16384 + so) =
+                in_sum ? make_uint4(src[o], src[o + 1], src[o + 2], src[o + 3]) : make_uint4(0, 0, 0, 0);
           }
         }
         fence_async_smem();
@@ -578,37 +607,11 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
 
 // ---------------------------------------------------------------------------
 // band kernel
-// Debug builds (-DSBL_TRACE) record clock64() at the phase boundaries of one query tile per CTA; the
-// regular build compiles the marks away.
-#ifdef SBL_TRACE
-__device__ long long g_band_trace[160][96];
-#define SBL_MARK(cond, slot)                                   \
-  do {                                                         \
-    if (cond) g_band_trace[blockIdx.x][slot] = clock64();      \
-  } while (0)
-constexpr int kTraceIt = 20;
-__device__ __forceinline__ long long trace_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define SBL_MARK_NS(cond, slot)                                \
-  do {                                                         \
-    if (cond) g_band_trace[blockIdx.x][slot] = trace_ns();     \
-  } while (0)
-#else
-#define SBL_MARK_NS(cond, slot) \
-  do {                          \
-  } while (0)
-#define SBL_MARK(cond, slot) \
-  do {                       \
-  } while (0)
-#endif
 struct BandArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_w, tm_phik, tm_kv, tm_out;
   SblParams p;
   const float* beta;
-  const float* ksum;
+  const float* ksum;     // (BH, 256) fp32, reference feature order
   const float* wmax;     // [1]: max_f |sqrt(tau) w_f| of the bf16 projection
   int* status;
   int ntq;               // query tiles per (b,h)
@@ -619,43 +622,51 @@ namespace band {
 constexpr int BQ = 128, KT = 128;
 constexpr int NCQ = 4;                     // column groups per row: a softmax thread owns 128/NCQ key columns of a tile
 constexpr int NSOFT = 128 * NCQ;           // softmax threads: warp w owns rows 32*(w%4).., column group w/4
-constexpr int WP = NSOFT / 32;             // first non-softmax warp: producer; WP+1: MMA (U, S, O, low-rank); WP+2: MMA (P)
-constexpr int NTHREADS = NSOFT + 96;
-constexpr uint32_t OFF_Q = 0;              // 16 KB [128 q][64 e]
-constexpr uint32_t OFF_KV = 16384;         // 32 KB [256 f][64 d]; its first 16 KB hold Wt [128 r][64 e] until U is computed
-constexpr uint32_t OFF_K = 49152;          // 16 KB [128 keys][64 e]
-constexpr uint32_t OFF_V = OFF_K + 16384;  // 16 KB [128 keys][64 d]
+constexpr int WSOFT = NSOFT / 32;          // softmax warps
+constexpr int W_LOADKV = WSOFT;            // producer: K, V, phi(K) tiles; output stores
+constexpr int W_LOADQ = WSOFT + 1;         // producer: Q tiles, halves of Wt, halves of KV
+constexpr int W_MMA_A = WSOFT + 2;         // MMA issuer: U halves, S, O, low-rank
+constexpr int W_MMA_B = WSOFT + 3;         // MMA issuer: P
+constexpr int NTHREADS = NSOFT + 128;
+constexpr uint32_t OFF_Q = 0;              // 2 x 16 KB [128 q][64 e]: current and next query tile
+constexpr uint32_t OFF_W = 32768;          // 8 KB [64 r][64 e]: one half of Wt at a time
+constexpr uint32_t OFF_KVH = 40960;        // 16 KB [128 f][64 d]: one feature half of KV at a time
+constexpr uint32_t OFF_K = 57344;          // 16 KB [128 keys][64 e]
+constexpr uint32_t OFF_V = OFF_K + 16384;  // 16 KB [128 keys][64 d]; also the staging buffer of the output tile
 constexpr uint32_t OFF_PK = OFF_V + 16384; // 2 x 64 KB: phi(K) tiles, each 4 blocks [128 keys][64 f]
 constexpr uint32_t OFF_MISC = OFF_PK + 2 * 65536;    // ksum fp32[256] + |q|^2 partials fp32[NSOFT] + exchange fp32[2][NSOFT]
 constexpr uint32_t OFF_BAR = OFF_MISC + 1024 + 12 * NSOFT;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;
-// tensor memory columns
-constexpr uint32_t T_PHIQ = 0;     // 128: phi(Q) packed bf16 (256 features)
-constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, later P of the same tile; U of the next query tile
-constexpr uint32_t T_O = 384;      // 64
-constexpr uint32_t T_D = 448;      // 64: D packed bf16 (128 keys)
+static_assert(SMEM_BYTES <= 232448, "dynamic shared memory of one CTA");
+// tensor memory columns (512): three 64-column feature-half slots, two 128-column S/E/D buffers, O
+__device__ __forceinline__ constexpr uint32_t hq_col(int slot) { return slot == 0 ? 0u : (slot == 1 ? 64u : 384u); }
+constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, then E, then D = E - P (fp32), then D packed bf16 in place
+constexpr uint32_t T_O = 448;      // 64
 // barrier indices
 enum {
-  B_Q = 0,       // Q tile landed                      (per query tile)
-  B_W,           // Wt landed                          (per query tile)
-  B_KV,          // KV landed                          (per query tile)
-  B_UQ,          // U = Q Wt^T computed                (per query tile)
-  B_PHIQ,        // phi(Q) stored, O read              (per query tile, one arrival per softmax warp)
-  B_DONE,        // all MMAs of the query tile done    (per query tile)
-  B_QFREE,       // Q buffer reusable                  (per query tile, 1 + one per softmax warp)
-  B_WFREE,       // Wt/KV buffer reusable              (per query tile)
-  B_DFREE,       // D consumed by O += D V             (per key tile)
-  B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY,              // per key tile, single buffers
-  B_PKFULL, B_PKEMPTY = B_PKFULL + 2,                // [2] per key tile, by ring slot
-  B_SFULL = B_PKEMPTY + 2,                           // [2] by buffer
-  B_ADONE = B_SFULL + 2,                             // [2] one arrival per softmax warp
-  B_PFULL = B_ADONE + 2,                             // [2]
-  B_BDONE = B_PFULL + 2,                             // [2] one arrival per softmax warp
-  B_SISS = B_BDONE + 2,                              // S of a third or later key tile has been issued (orders P behind it)
-  B_OFULL,                                           // output tile staged in shared memory (one arrival per softmax warp)
+  B_QFULL = 0,                    // [2] Q tile landed                                   (by query tile parity)
+  B_QFREE = B_QFULL + 2,          // [2] Q buffer reusable: last MMA reading it + one arrival per softmax warp
+  B_WFULL = B_QFREE + 2,          // half of Wt landed                                   (per load)
+  B_WFREE,                        // U half computed: the Wt buffer is reusable
+  B_KVFULL,                       // half of KV landed                                   (per load)
+  B_KVFREE,                       // low-rank product done with it
+  B_UQFULL,                       // [3] U half computed into the slot
+  B_PHIFULL = B_UQFULL + 3,       // [3] features formed in the slot (one arrival per softmax warp)
+  B_HQFREE = B_PHIFULL + 3,       // [3] slot reusable: issuer A (low-rank) and issuer B (last P) both done
+  B_KFULL = B_HQFREE + 3, B_KEMPTY, B_VFULL, B_VEMPTY,   // per key tile, single buffers
+  B_PKFULL, B_PKEMPTY = B_PKFULL + 2,                    // [2] per key tile, by ring slot
+  B_SFULL = B_PKEMPTY + 2,        // [2] by buffer
+  B_ADONE = B_SFULL + 2,          // [2] one arrival per softmax warp
+  B_PFULL = B_ADONE + 2,          // [2]
+  B_BDONE = B_PFULL + 2,          // [2] one arrival per softmax warp
+  B_BUFFREE = B_BDONE + 2,        // [2] O += D V done: the buffer may take the next S
+  B_OFREE = B_BUFFREE + 2,        // O read by the epilogue (one arrival per softmax warp)
+  B_DONE,                         // all MMAs of the query tile done
+  B_OFULL,                        // output tile staged in shared memory (one arrival per softmax warp)
+  B_OSTORED,                      // the bulk store of the staged tile has read the staging buffer
   B_COUNT
 };
-static_assert(B_COUNT <= 32, "one barrier per lane of the initialising warp");
+static_assert(B_COUNT <= 60, "barriers and the tensor-memory slot share 512 bytes");
 }  // namespace band
 
 // Geometry of one 128-query tile: which key tiles it visits.
@@ -713,17 +724,18 @@ struct PkTrack {
   }
 };
 
-// Persistent: CTA c processes a run of consecutive query tiles.  Key tiles are numbered
-// per CTA (g = 0, 1, ... across query tiles); key tile g uses accumulator buffer g & 1, and the U of a
-// query tile goes to the buffer its second key tile will use, so that the next query tile's Q/Wt loads
-// and U = Q Wt^T overlap the current tile's tail.
-__global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_constant__ BandArgs a) {
+// Persistent: CTA c processes a run of consecutive query tiles.  Key tiles are numbered per CTA
+// (g = 0, 1, ... across query tiles) and key tile g uses buffer g & 1; feature half h of the run's
+// query tile `it` uses slot (2 it + h) % 3, use number (2 it + h) / 3 of that slot.  Both halves of
+// tile it + 1 are formed while tile it is processed: half 0 in the slot tile it does not use, half 1
+// in the slot of tile it's half 0 as soon as the last P product has read that.
+__global__ void __launch_bounds__(band::NTHREADS, 1) tc_band_kernel(const __grid_constant__ BandArgs a) {
   using namespace band;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
-  float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 62);
+  float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);   // [256], internal feature order
   float* s_sq = s_ksum + kM;        // [NSOFT]
   float* s_xch = s_sq + NSOFT;      // [2][NSOFT]
 
@@ -734,15 +746,19 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   const int tile_lo = (int)((int64_t)a.ntiles * blockIdx.x / gridDim.x);
   const int n_it = (int)((int64_t)a.ntiles * (blockIdx.x + 1) / gridDim.x) - tile_lo;
 
-  if (warp == WP + 1) {
-    if (lane < B_COUNT) {
-      const bool soft = lane == B_PHIQ || lane == B_OFULL || lane == B_ADONE || lane == B_ADONE + 1 || lane == B_BDONE || lane == B_BDONE + 1;
-      // the softmax warps arrive once per warp
-      mbar_init(bars + lane, lane == B_QFREE ? WP + 1 : (soft ? WP : 1));
+  if (warp == W_MMA_A) {
+    for (int i = lane; i < B_COUNT; i += 32) {
+      const bool soft = (i >= B_PHIFULL && i < B_PHIFULL + 3) || (i >= B_ADONE && i < B_ADONE + 2) ||
+                        (i >= B_BDONE && i < B_BDONE + 2) || i == B_OFREE || i == B_OFULL;
+      int count = 1;
+      if (soft) count = WSOFT;                                   // the softmax warps arrive once per warp
+      if (i >= B_QFREE && i < B_QFREE + 2) count = WSOFT + 1;
+      if (i >= B_HQFREE && i < B_HQFREE + 3) count = 2;
+      mbar_init(bars + i, count);
     }
     fence_mbar_init();
   }
-  if (warp == WP) {
+  if (warp == W_LOADKV) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -753,41 +769,19 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
   // column 0; keeping the base a compile-time constant keeps every MMA operand uniform.
   constexpr uint32_t tb = 0;
   if (tid == 0 && *tmem_slot != 0) atomicCAS(a.status, 0, 40);
-  SBL_MARK(tid == 0, 70);
-  SBL_MARK_NS(tid == 0, 72);
 
-  if (warp == WP) {
-    // ---------------- producer (whole warp waits, one lane issues) ----------------
+  if (warp == W_LOADKV) {
+    // ---------------- producer 1: K, phi(K), V tiles, output stores (whole warp waits, one lane issues) ------
     const bool leader = elect_one();
     if (leader) {
-      prefetch_tmap(&a.tm_q);
       prefetch_tmap(&a.tm_k);
       prefetch_tmap(&a.tm_v);
-      prefetch_tmap(&a.tm_w);
       prefetch_tmap(&a.tm_phik);
-      prefetch_tmap(&a.tm_kv);
       prefetch_tmap(&a.tm_out);
     }
     int gk = 0;   // key tiles loaded so far
     PkTrack pk;
-    // Q and Wt of query tile `it2`: issued as soon as the previous tile has released the two buffers,
-    // i.e. in the middle of the previous tile, so that U = Q Wt^T of the next tile is ready at its start
-    TileCursor cur(a, tile_lo), cur_next(a, tile_lo);
-    auto load_qw = [&](int it2) {   // called once per it2, in order: cur_next is the cursor of tile it2
-      if (it2 >= n_it) return;
-      const BandTile T2 = band_tile(a, cur_next);
-      cur_next.next(a);
-      if (it2 >= 1) mbar_wait(bars + B_QFREE, (it2 - 1) & 1, a.status, 20);
-      if (leader) {
-        mbar_expect_tx(bars + B_Q, 16384);
-        tma_load_4d(smem + OFF_Q, &a.tm_q, bars + B_Q, 0, T2.i0, T2.h, T2.b);
-      }
-      if (it2 >= 1) mbar_wait(bars + B_WFREE, (it2 - 1) & 1, a.status, 21);
-      if (leader) {
-        mbar_expect_tx(bars + B_W, 16384);
-        tma_load_2d(smem + OFF_KV, &a.tm_w, bars + B_W, 0, 0);
-      }
-    };
+    TileCursor cur(a, tile_lo);
     // The softmax warps stage a finished output tile in the V buffer (free once the tile's last O += D V has
     // run); one bulk store writes it out.  The next V load waits until the store has read the buffer.
     int o_i0 = 0, o_h = 0, o_b = 0;
@@ -797,10 +791,10 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         tma_store_4d(&a.tm_out, smem + OFF_V, 0, o_i0, o_h, o_b);
         tma_store_commit();
         tma_store_wait_read0();
+        mbar_arrive(bars + B_OSTORED);
       }
       __syncwarp();
     };
-    load_qw(0);
     for (int it = 0; it < n_it; ++it, cur.next(a)) {
       const BandTile T = band_tile(a, cur);
       // K and V are single-buffered, phi(K) double-buffered.  Issue order follows the order
@@ -811,14 +805,6 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         if (leader) {
           mbar_expect_tx(bars + B_VFULL, 16384);
           tma_load_4d(smem + OFF_V, &a.tm_v, bars + B_VFULL, 0, T.j0 + t * KT, T.h, T.b);
-        }
-      };
-      auto load_kv = [&]() {
-        // KV shares its buffer with Wt: load it once U = Q Wt^T has been computed
-        mbar_wait(bars + B_UQ, it & 1, a.status, 24);
-        if (leader) {
-          mbar_expect_tx(bars + B_KV, 32768);
-          tma_load_3d(smem + OFF_KV, &a.tm_kv, bars + B_KV, 0, 0, T.bh);
         }
       };
       // The last key tile of a query tile is the one no earlier tile of the run has touched, and its V is
@@ -849,16 +835,13 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         }
         // V(0) is not needed before the first O += D V; its buffer holds the previous tile's staged output
         // until that tile's epilogue, which must not hold up the K tile S(1) is waiting for
-        if (t == 0) {
-          load_kv();
-        } else if (t == 1) {
+        if (t == 1) {
           if (it >= 1) store_out(it - 1);
           load_v(0);
-        } else {
+        } else if (t >= 2) {
           load_v(t - 1);
         }
       }
-      if (T.nt == 0) load_kv();
       if (T.nt <= 1) {
         if (it >= 1) store_out(it - 1);
         if (T.nt == 1) load_v(0);
@@ -866,117 +849,202 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
       o_i0 = T.i0;
       o_h = T.h;
       o_b = T.b;
-      load_qw(it + 1);
       if (T.nt >= 2) load_v(T.nt - 1);
       gk += T.nt;
     }
     store_out(n_it - 1);
     if (leader) tma_store_wait_all();
     __syncwarp();
-  } else if (warp == WP + 1) {
-    // ---------------- MMA issuer A: U, S, low-rank, O (whole warp waits, one lane issues) ----------------
+  } else if (warp == W_LOADQ) {
+    // ---------------- producer 2: Q tiles, halves of Wt, halves of KV ----------------
+    // Load order = the order in which issuer A consumes them; every wait below is released by an MMA group
+    // that issuer A reaches without needing a later load of this warp.
     const bool leader = elect_one();
-    constexpr uint32_t id_n128 = idesc_bf16(128, 128, false, false);
+    if (leader) {
+      prefetch_tmap(&a.tm_q);
+      prefetch_tmap(&a.tm_w);
+      prefetch_tmap(&a.tm_kv);
+    }
+    TileCursor cq0(a, tile_lo), cq1(a, tile_lo), cq2(a, tile_lo);   // cursors of tiles it, it + 1, it + 2
+    cq1.next(a);
+    cq2.next(a);
+    cq2.next(a);
+    auto load_q = [&](int itx, const TileCursor& c) {
+      const BandTile Tx = band_tile(a, c);
+      if (leader) {
+        mbar_expect_tx(bars + B_QFULL + (itx & 1), 16384);
+        tma_load_4d(smem + OFF_Q + (itx & 1) * 16384, &a.tm_q, bars + B_QFULL + (itx & 1), 0, Tx.i0, Tx.h, Tx.b);
+      }
+    };
+    auto load_w = [&](int idx) {      // load number idx = 2 it + half
+      if (idx >= 1) mbar_wait(bars + B_WFREE, (idx - 1) & 1, a.status, 50);
+      if (leader) {
+        mbar_expect_tx(bars + B_WFULL, 8192);
+        tma_load_2d(smem + OFF_W, &a.tm_w, bars + B_WFULL, 0, 64 * (idx & 1));
+      }
+    };
+    auto load_kv = [&](int idx, int bh) {
+      if (idx >= 1) mbar_wait(bars + B_KVFREE, (idx - 1) & 1, a.status, 51);
+      if (leader) {
+        mbar_expect_tx(bars + B_KVFULL, 16384);
+        tma_load_3d(smem + OFF_KVH, &a.tm_kv, bars + B_KVFULL, 0, 128 * (idx & 1), bh);
+      }
+    };
+    load_q(0, cq0);
+    load_w(0);
+    load_kv(0, cq0.bh);
+    if (n_it > 1) load_q(1, cq1);
+    load_w(1);
+    for (int it = 0; it < n_it; ++it) {
+      const bool have_next = it + 1 < n_it;
+      if (have_next) load_w(2 * it + 2);
+      load_kv(2 * it + 1, cq0.bh);
+      if (have_next) load_w(2 * it + 3);
+      if (it + 2 < n_it) {
+        mbar_wait(bars + B_QFREE + (it & 1), (it >> 1) & 1, a.status, 20);
+        load_q(it + 2, cq2);
+      }
+      if (have_next) load_kv(2 * it + 2, cq1.bh);
+      cq0.next(a);
+      cq1.next(a);
+      cq2.next(a);
+    }
+    __syncwarp();
+  } else if (warp == W_MMA_A) {
+    // ---------------- MMA issuer A: U halves, S, O, low-rank (whole warp waits, one lane issues) ----------------
+    const bool leader = elect_one();
+    constexpr uint32_t id_s = idesc_bf16(128, 128, false, false);
+    constexpr uint32_t id_u = idesc_bf16(128, 64, false, false);
     constexpr uint32_t id_o = idesc_bf16(128, 64, false, true);
-    const uint64_t dQ = smem_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
-    const uint64_t dKV = smem_desc_sw128(smem_u32(smem + OFF_KV), 16, 1024);
+    const uint64_t dQ0 = smem_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
+    const uint64_t dW = smem_desc_sw128(smem_u32(smem + OFF_W), 16, 1024);
+    const uint64_t dKVH = smem_desc_sw128(smem_u32(smem + OFF_KVH), 16, 1024);
     const uint64_t dK0 = smem_desc_sw128(smem_u32(smem + OFF_K), 16, 1024);
     const uint64_t dV0 = smem_desc_sw128(smem_u32(smem + OFF_V), 16, 1024);
-    int gk = 0;
-    auto b_done_wait = [&](int g) {   // B of key tile g finished: its buffer and D are consumed
-      mbar_wait(bars + B_BDONE + (g & 1), (g >> 1) & 1, a.status, 28);
-    };
-    // tell_b: issuer B holds P of the previous key tile back until this S is in the queue, so that the
-    // softmax warps get their next S before the (four times longer) P
-    auto issue_s = [&](int g, bool last, bool tell_b) {
-      mbar_wait(bars + B_KFULL, g & 1, a.status, 25);
+    // U half `half` of run tile itx (its Q tile must have landed) into its slot
+    auto issue_u = [&](int itx, int half) {
+      const int idx = 2 * itx + half, s = idx % 3, u = idx / 3;
+      if (u >= 1) mbar_wait(bars + B_HQFREE + s, (u - 1) & 1, a.status, 52);
+      mbar_wait(bars + B_WFULL, idx & 1, a.status, 53);
       tc_fence_after_sync();
       if (leader) {
-        const uint32_t td = tb + T_BUF + (g & 1) * 128;
-        mma_ss(td, dQ, dK0, id_n128, false);
-        mma_ss(td, dQ + 2, dK0 + 2, id_n128, true);
-        mma_ss(td, dQ + 4, dK0 + 4, id_n128, true);
-        mma_ss(td, dQ + 6, dK0 + 6, id_n128, true);
-        mma_commit(bars + B_KEMPTY);
-        mma_commit(bars + B_SFULL + (g & 1));
-        if (last) mma_commit(bars + B_QFREE);   // no later MMA of this query tile reads Q
-        if (tell_b) mbar_arrive(bars + B_SISS);
+        const uint32_t td = tb + hq_col(s);
+        const uint64_t dQ = dQ0 + (uint64_t)((itx & 1) * (16384 >> 4));
+        mma_ss(td, dQ, dW, id_u, false);
+        mma_ss(td, dQ + 2, dW + 2, id_u, true);
+        mma_ss(td, dQ + 4, dW + 4, id_u, true);
+        mma_ss(td, dQ + 6, dW + 6, id_u, true);
+        mma_commit(bars + B_UQFULL + s);
+        mma_commit(bars + B_WFREE);
       }
       __syncwarp();
     };
+    // S of key tile g (query tile in Q buffer qb); last: no later MMA reads that Q buffer
+    auto issue_s = [&](int g, int qb, bool last) {
+      mbar_wait(bars + B_KFULL, g & 1, a.status, 25);
+      if (g >= 2) mbar_wait(bars + B_BUFFREE + (g & 1), ((g - 2) >> 1) & 1, a.status, 28);
+      tc_fence_after_sync();
+      if (leader) {
+        const uint32_t td = tb + T_BUF + (g & 1) * 128;
+        const uint64_t dQ = dQ0 + (uint64_t)(qb * (16384 >> 4));
+        mma_ss(td, dQ, dK0, id_s, false);
+        mma_ss(td, dQ + 2, dK0 + 2, id_s, true);
+        mma_ss(td, dQ + 4, dK0 + 4, id_s, true);
+        mma_ss(td, dQ + 6, dK0 + 6, id_s, true);
+        mma_commit(bars + B_KEMPTY);
+        mma_commit(bars + B_SFULL + (g & 1));
+        if (last) mma_commit(bars + B_QFREE + qb);
+      }
+      __syncwarp();
+    };
+    // O += D V: D packed bf16 sits in the first 16 of every 32 columns of the buffer
     auto issue_o = [&](int g) {
-      b_done_wait(g);
+      mbar_wait(bars + B_BDONE + (g & 1), (g >> 1) & 1, a.status, 29);
       mbar_wait(bars + B_VFULL, g & 1, a.status, 29);
+      tc_fence_after_sync();
+      if (leader) {
+        const uint32_t ta = tb + T_BUF + (g & 1) * 128;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_ts(tb + T_O, ta + 32 * (k >> 1) + 8 * (k & 1), dV0 + (uint64_t)(k * (2048 >> 4)), id_o, true);
+        mma_commit(bars + B_VEMPTY);
+        mma_commit(bars + B_BUFFREE + (g & 1));
+      }
+      __syncwarp();
+    };
+    // O (+)= phi(Q)[half] KV[half]; half 0 comes first in a tile and initialises O
+    auto issue_lr = [&](int itx, int half) {
+      const int idx = 2 * itx + half, s = idx % 3, u = idx / 3;
+      mbar_wait(bars + B_PHIFULL + s, u & 1, a.status, 31);
+      mbar_wait(bars + B_KVFULL, idx & 1, a.status, 32);
+      if (half == 0 && itx >= 1) mbar_wait(bars + B_OFREE, (itx - 1) & 1, a.status, 54);
       tc_fence_after_sync();
       if (leader) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          mma_ts(tb + T_O, tb + T_D + k * 8, dV0 + (uint64_t)(k * (2048 >> 4)), id_o, true);
-        mma_commit(bars + B_VEMPTY);
-        mma_commit(bars + B_DFREE);
+          mma_ts(tb + T_O, tb + hq_col(s) + k * 8, dKVH + (uint64_t)(k * (2048 >> 4)), id_o, half != 0 || k > 0);
+        mma_commit(bars + B_KVFREE);
+        mma_commit(bars + B_HQFREE + s);
       }
       __syncwarp();
     };
-    TileCursor cur(a, tile_lo);
-    for (int it = 0; it < n_it; ++it, cur.next(a)) {
+    TileCursor cur(a, tile_lo), cur_n(a, tile_lo);
+    cur_n.next(a);
+    int gk = 0;
+    bool s0_issued = false;   // S(0) of the coming tile was issued during the previous tile
+    {
+      const BandTile T0 = band_tile(a, cur);
+      mbar_wait(bars + B_QFULL, 0, a.status, 30);
+      issue_u(0, 0);
+      issue_u(0, 1);
+      if (T0.nt == 0 && leader) mma_commit(bars + B_QFREE);
+      __syncwarp();
+    }
+    for (int it = 0; it < n_it; ++it, cur.next(a), cur_n.next(a)) {
       const BandTile T = band_tile(a, cur);
-      const int nt = T.nt;
-      // U = Q Wt^T into the buffer of key tile gk+1; that buffer last held key tile gk-1
-      mbar_wait(bars + B_Q, it & 1, a.status, 30);
-      mbar_wait(bars + B_W, it & 1, a.status, 30);
-      if (gk >= 1) b_done_wait(gk - 1);
-      tc_fence_after_sync();
-      if (leader) {
-        const uint32_t td = tb + T_BUF + ((gk + 1) & 1) * 128;
-        mma_ss(td, dQ, dKV, id_n128, false);
-        mma_ss(td, dQ + 2, dKV + 2, id_n128, true);
-        mma_ss(td, dQ + 4, dKV + 4, id_n128, true);
-        mma_ss(td, dQ + 6, dKV + 6, id_n128, true);
-        mma_commit(bars + B_UQ);
-        if (nt == 0) mma_commit(bars + B_QFREE);
-        SBL_MARK(it == kTraceIt, 20);
+      const int nt = T.nt, qb = it & 1;
+      const bool have_next = it + 1 < n_it;
+      int nt_n = 0;
+      if (have_next) nt_n = band_tile(a, cur_n).nt;
+      if (nt > 0 && !s0_issued) issue_s(gk, qb, nt == 1);
+      if (nt > 1) issue_s(gk + 1, qb, nt == 2);
+      s0_issued = false;
+      issue_lr(it, 0);
+      if (have_next) {
+        mbar_wait(bars + B_QFULL + (qb ^ 1), ((it + 1) >> 1) & 1, a.status, 30);
+        issue_u(it + 1, 0);
       }
-      __syncwarp();
-      // S(0) does not need phi(Q): it runs while the softmax warps form it (its buffer last held key tile gk-2)
-      if (nt > 0) {
-        if (gk >= 2) b_done_wait(gk - 2);
-        issue_s(gk, nt == 1, false);
-        SBL_MARK(leader && it == kTraceIt, 21);
-      }
-      mbar_wait(bars + B_PHIQ, it & 1, a.status, 31);
-      tc_fence_after_sync();
-      SBL_MARK(leader && it == kTraceIt, 22);
-      if (nt > 1) issue_s(gk + 1, nt == 2, false);
-      SBL_MARK(leader && it == kTraceIt, 23);
-      // O starts as the low-rank numerator phi(Q) KV; the band tiles accumulate onto it
-      mbar_wait(bars + B_KV, it & 1, a.status, 32);
-      tc_fence_after_sync();
-      if (leader) {
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-          mma_ts(tb + T_O, tb + T_PHIQ + k * 8, dKV + (uint64_t)(k * (2048 >> 4)), id_o, k > 0);
-        mma_commit(bars + B_WFREE);
-        SBL_MARK(it == kTraceIt, 24);
-      }
-      __syncwarp();
-      for (int t = 1; t < nt; ++t) {
-        // both need B(t-1) finished; S first, the softmax warps are waiting for it
-        if (t + 1 < nt) {
-          b_done_wait(gk + t - 1);
-          issue_s(gk + t + 1, t + 2 == nt, true);
-          SBL_MARK(leader && it == kTraceIt, 25);
+      // S(0) of the next tile as soon as its buffer is free: the softmax warps start that tile with it
+      auto early_s = [&]() {
+        if (have_next && nt_n > 0) {
+          issue_s(gk + nt, qb ^ 1, nt_n == 1);
+          s0_issued = true;
         }
-        issue_o(gk + t - 1);
-        SBL_MARK(leader && it == kTraceIt && t < 3, 25 + t);
+      };
+      // second feature half of the next tile (its slot is released by this tile's last P over half 0), then this
+      // tile's second low-rank half: both ahead of the last O += D V, which waits longest
+      auto tail = [&]() {
+        if (have_next) {
+          issue_u(it + 1, 1);
+          if (nt_n == 0 && leader) mma_commit(bars + B_QFREE + (qb ^ 1));
+          __syncwarp();
+        }
+        issue_lr(it, 1);
+      };
+      if (nt < 2) early_s();
+      for (int t = 0; t < nt; ++t) {
+        if (t == nt - 1) tail();
+        issue_o(gk + t);
+        if (t + 2 < nt) issue_s(gk + t + 2, qb, t + 3 == nt);
+        if (t + 2 == nt) early_s();
       }
-      if (nt > 0) issue_o(gk + nt - 1);
-      SBL_MARK(leader && it == kTraceIt, 28);
+      if (nt == 0) tail();
       if (leader) mma_commit(bars + B_DONE);
       __syncwarp();
       gk += nt;
     }
-  } else if (warp == WP + 2) {
-    // ---------------- MMA issuer B: buffer(g) -= phi(Q) phi(K)^T ----------------
+  } else if (warp == W_MMA_B) {
+    // ---------------- MMA issuer B: buffer(g) -= phi(Q) phi(K)^T, one product per feature half ----------------
     // The buffer holds E = exp(tau S - pls) written back by the softmax warps; the product is accumulated
     // with the A operand negated, which leaves D = E - P in fp32.
     // (its own warp, on another scheduler than issuer A: the two issue streams run in parallel)
@@ -986,34 +1054,54 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     int gk = 0;
     PkTrack pk;
     TileCursor cur(a, tile_lo);
-    int nsiss = 0;
     for (int it = 0; it < n_it; ++it, cur.next(a)) {
       const BandTile T = band_tile(a, cur);
-      mbar_wait(bars + B_PHIQ, it & 1, a.status, 39);
+      const int s0 = (2 * it) % 3, u0 = (2 * it) / 3, s1 = (2 * it + 1) % 3, u1 = (2 * it + 1) / 3;
+      if (T.nt == 0) {
+        // nothing to multiply: release both slots, but only once their features exist, so that this warp
+        // can never be a whole use of a slot ahead of issuer A
+        mbar_wait(bars + B_PHIFULL + s0, u0 & 1, a.status, 39);
+        mbar_wait(bars + B_PHIFULL + s1, u1 & 1, a.status, 39);
+        if (leader) {
+          mbar_arrive(bars + B_HQFREE + s0);
+          mbar_arrive(bars + B_HQFREE + s1);
+        }
+        __syncwarp();
+        continue;
+      }
       for (int t = 0; t < T.nt; ++t) {
         const int g = gk + t, s = g & 1;
         const int kt = T.j0 / KT + t, ps = kt & 1;
+        const bool last = t == T.nt - 1;
         mbar_wait(bars + B_ADONE + s, (g >> 1) & 1, a.status, 26);
-        SBL_MARK(leader && it == kTraceIt && t < 3, 34 + t);
         if (!pk.resident(ps, T.bh, kt)) {   // a tile still resident from the previous query tile was waited for then
           mbar_wait(bars + B_PKFULL + ps, pk.fills(ps) & 1, a.status, 27);
           pk.filled(ps, T.bh, kt);
         }
         pk.used(ps);
-        if (t >= 1 && t + 1 < T.nt) {   // S(t+1) goes first
-          mbar_wait(bars + B_SISS, nsiss & 1, a.status, 41);
-          ++nsiss;
-        }
+        if (t == 0) mbar_wait(bars + B_PHIFULL + s0, u0 & 1, a.status, 39);
         tc_fence_after_sync();
+        const uint64_t dPK = dPK0 + (uint64_t)(ps * (65536 >> 4));
+        const uint32_t td = tb + T_BUF + s * 128;
         if (leader) {
-          const uint64_t dPK = dPK0 + (uint64_t)(ps * (65536 >> 4));
-          const uint32_t td = tb + T_BUF + s * 128;
 #pragma unroll
-          for (int k = 0; k < 16; ++k)
-            mma_ts(td, tb + T_PHIQ + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_neg, true);
+          for (int k = 0; k < 8; ++k)
+            mma_ts(td, tb + hq_col(s0) + k * 8, dPK + (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2), id_neg, true);
+          if (last) mma_commit(bars + B_HQFREE + s0);
+        }
+        __syncwarp();
+        if (t == 0) {
+          mbar_wait(bars + B_PHIFULL + s1, u1 & 1, a.status, 39);
+          tc_fence_after_sync();
+        }
+        if (leader) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_ts(td, tb + hq_col(s1) + k * 8, dPK + (uint64_t)((2 + (k >> 2)) * (16384 >> 4) + (k & 3) * 2), id_neg,
+                   true);
+          if (last) mma_commit(bars + B_HQFREE + s1);
           mma_commit(bars + B_PKEMPTY + ps);
           mma_commit(bars + B_PFULL + s);
-          SBL_MARK(it == kTraceIt && t < 3, 30 + t);
         }
         __syncwarp();
       }
@@ -1025,77 +1113,76 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
     const int qd = warp & 3, cq = warp >> 2;         // lane quarter (rows), column group
     const int row = qd * 32 + lane;                  // query row of this thread
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
-    constexpr int PW = 128 / NCQ;                    // projections (and key columns per tile) owned by this thread
     constexpr int OW = 64 / NCQ;                     // output columns owned by this thread
-    const int c0 = PW * cq;                          // first key column (of every key tile) of this thread
+    const int c0 = 32 * cq;                          // first key column (of every key tile) of this thread
     const float wmax = __ldg(a.wmax);
     const float half_log_m = 0.5f * logf((float)kM);
     const float sc = p.softmax_temp * kLog2e;
-    int gk = 0, bh_smem = -1;
-    TileCursor cur(a, tile_lo);
-    for (int it = 0; it < n_it; ++it, cur.next(a)) {
-      const BandTile T = band_tile(a, cur);
-      const int nt = T.nt;
-      const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
-      const float beta = __ldg(a.beta + T.bh);       // needed after phi(Q): the load has a whole phase to land
-#ifdef SBL_TRACE
-      const bool tr = it == kTraceIt && lane == 0 && (warp == 0 || warp == 15);
-      const int trb = warp == 0 ? 0 : 48;
-#endif
-      SBL_MARK(tr, trb + 0);
-      // s_ksum is free again: every thread passed the exchange of the previous tile
-      if (T.bh != bh_smem) {
-        for (int i = tid; i < kM; i += NSOFT) s_ksum[i] = a.ksum[(int64_t)T.bh * kM + i];
-        bh_smem = T.bh;
-      }
-      // ---- |q|^2: the four threads of a row each sum 16 of its 64 elements ----
-      mbar_wait(bars + B_Q, it & 1, a.status, 33);
-      SBL_MARK(tr, trb + 1);
-      s_sq[tid] = quarter_row_sumsq_sw128(smem + OFF_Q, row, cq);
-      warp_arrive(bars + B_QFREE, lane);
+    // Row norm, stabiliser and the summary row of run tile itx (its Q tile must be on its way):
+    // gq = tau |q|^2 / 2, M = wmax |q| >= |u_f| for every projection (Cauchy-Schwarz)
+    auto prep_tile = [&](int itx, const BandTile& Tx, float& M, float& gq) {
+      if (tid < kM) s_ksum[tid] = __ldg(a.ksum + (int64_t)Tx.bh * kM + feat_of_slot(tid));
+      mbar_wait(bars + B_QFULL + (itx & 1), (itx >> 1) & 1, a.status, 33);
+      s_sq[tid] = quarter_row_sumsq_sw128(smem + OFF_Q + (itx & 1) * 16384, row, cq);
+      warp_arrive(bars + B_QFREE + (itx & 1), lane);
       asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
       const float qn2 = (s_sq[row] + s_sq[128 + row]) + (s_sq[256 + row] + s_sq[384 + row]);
-      const float g = 0.5f * p.softmax_temp * qn2;
-      const float M = sqrtf(qn2) * wmax;             // >= |u_f| for every feature (Cauchy-Schwarz)
-      SBL_MARK(tr, trb + 2);
-      // ---- phi(Q): this thread's PW projections -> 2*PW features ----
-      mbar_wait(bars + B_UQ, it & 1, a.status, 34);
+      gq = 0.5f * p.softmax_temp * qn2;
+      M = sqrtf(qn2) * wmax;
+    };
+    // Features of one half, in place: this thread's 16 projections (16 fp32 columns) become 16 "+" and 16 "-"
+    // features (2 x 8 packed columns); z accumulates phi(Q) . sum phi(K) over them.
+    auto form_half = [&](int itx, int half, float M, float& z) {
+      const int idx = 2 * itx + half, s = idx % 3, u = idx / 3;
+      mbar_wait(bars + B_UQFULL + s, u & 1, a.status, 34);
       tc_fence_after_sync();
-      SBL_MARK(tr, trb + 3);
-      float2 zp = make_float2(0.f, 0.f), zm = make_float2(0.f, 0.f);
-      {
-        const float mo = -M * kLog2e;
-        const float2 mo2 = make_float2(mo, mo);
-        const float2 lp = make_float2(kLog2e, kLog2e), lm = make_float2(-kLog2e, -kLog2e);
-        const uint32_t t_uq = lane_base + T_BUF + ((gk + 1) & 1) * 128;
+      const uint32_t taddr = lane_base + hq_col(s) + 16 * cq;
+      const float* ks = s_ksum + 128 * half + 32 * cq;
+      const float mo = -M * kLog2e;
+      const float2 mo2 = make_float2(mo, mo);
+      const float2 lp = make_float2(kLog2e, kLog2e), lm = make_float2(-kLog2e, -kLog2e);
+      uint32_t r[16];
+      tmem_ld16(taddr, r);
+      tmem_ld_wait();
+      uint32_t p1[8], p2[8];
+      float2 zz = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int f0 = c0 + 16 * c;                // first projection index of this group of 16
-          uint32_t r[16];
-          tmem_ld16(t_uq + f0, r);
-          tmem_ld_wait();
-          uint32_t p1[8], p2[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float2 u = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            const float2 ap = fma2(u, lp, mo2), am = fma2(u, lm, mo2);
-            const float2 ep = make_float2(ex2(ap.x), ex2(ap.y));
-            const float2 em = make_float2(ex2(am.x), ex2(am.y));
-            p1[j] = pack_bf16(ep.x, ep.y);
-            p2[j] = pack_bf16(em.x, em.y);
-            zp = fma2(ep, *reinterpret_cast<const float2*>(s_ksum + f0 + 2 * j), zp);
-            zm = fma2(em, *reinterpret_cast<const float2*>(s_ksum + kR + f0 + 2 * j), zm);
-          }
-          tmem_st8(lane_base + T_PHIQ + f0 / 2, p1);
-          tmem_st8(lane_base + T_PHIQ + 64 + f0 / 2, p2);
-        }
-        tmem_st_wait();
+      for (int j = 0; j < 8; ++j) {
+        const float2 uu = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        const float2 ap = fma2(uu, lp, mo2), am = fma2(uu, lm, mo2);
+        const float2 ep = make_float2(ex2(ap.x), ex2(ap.y));
+        const float2 em = make_float2(ex2(am.x), ex2(am.y));
+        p1[j] = pack_bf16(ep.x, ep.y);
+        p2[j] = pack_bf16(em.x, em.y);
+        zz = fma2(ep, *reinterpret_cast<const float2*>(ks + 2 * j), zz);
+        zz = fma2(em, *reinterpret_cast<const float2*>(ks + 16 + 2 * j), zz);
       }
+      tmem_st8(taddr, p1);
+      tmem_st8(taddr + 8, p2);
+      tmem_st_wait();
       tc_fence_before_sync();
-      warp_arrive(bars + B_PHIQ, lane);
-      SBL_MARK(tr, trb + 4);
+      warp_arrive(bars + B_PHIFULL + s, lane);
+      z += zz.x + zz.y;
+    };
 
-      const float pls = (-g + M - half_log_m) + beta;               // query log-scale + key log-scale
+    int gk = 0;
+    TileCursor cur(a, tile_lo), cur_n(a, tile_lo);
+    cur_n.next(a);
+    float M_c, gq_c, z_c = 0.f;       // current tile: stabiliser, tau |q|^2 / 2, phi(Q) . sum phi(K) (this thread's share)
+    float M_n = 0.f, gq_n = 0.f, z_n = 0.f;
+    {
+      const BandTile T0 = band_tile(a, cur);
+      prep_tile(0, T0, M_c, gq_c);
+      form_half(0, 0, M_c, z_c);
+      form_half(0, 1, M_c, z_c);
+    }
+    for (int it = 0; it < n_it; ++it, cur.next(a), cur_n.next(a)) {
+      const BandTile T = band_tile(a, cur);
+      const int nt = T.nt;
+      const bool have_next = it + 1 < n_it;
+      const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
+      const float beta = __ldg(a.beta + T.bh);
+      const float pls = (-gq_c + M_c - half_log_m) + beta;          // query log-scale + key log-scale
       const float2 sc2 = make_float2(sc, sc);
       const float2 co2 = make_float2(-pls * kLog2e, -pls * kLog2e);  // exp(tau s - pls) = ex2(s * sc + co)
       float L = 0.f, sd = 0.f;   // row sums over this thread's columns: exponentials; D = E - P
@@ -1116,100 +1203,120 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         G.all = __all_sync(0xFFFFFFFFu, G.vis == 0xFFFFFFFFu);
         return G;
       };
-      Geo Gb, Ga;   // geometry of the tile phase B works on / phase A works on
-      // Software pipeline over key tiles: A(t+1) (exponentials of S, written back over S) runs while the
-      // tensor core subtracts P(t) from the buffer of tile t; B(t) then packs D(t).
-      for (int t = -1; t < nt; ++t) {
-        if (t + 1 < nt) {
-          // A: S(t+1) -> E = exp(tau S - pls) in place (fp32), row sum L
-          const int gg = gk + t + 1, s = gg & 1;
-          Ga = geometry(t + 1);
-          mbar_wait(bars + B_SFULL + s, (gg >> 1) & 1, a.status, 35);
-          tc_fence_after_sync();
-          SBL_MARK(tr && t + 1 < 3, trb + 5 + 4 * (t + 1));
-          if (!Ga.none) {   // a chunk nobody sees is left as it is: B writes zeros for it
-            const uint32_t tcol = lane_base + T_BUF + s * 128 + c0;
-            uint32_t rs[32];
-            tmem_ld32(tcol, rs);
-            tmem_ld_wait();
-            float2 l2 = make_float2(0.f, 0.f);
-            if (Ga.all) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float2 x =
-                    fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
-                const float2 e = make_float2(ex2(x.x), ex2(x.y));
-                l2 = add2(l2, e);
-                rs[2 * j] = __float_as_uint(e.x);
-                rs[2 * j + 1] = __float_as_uint(e.y);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float2 x =
-                    fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
-                const float2 ee = make_float2(ex2(x.x), ex2(x.y));
-                const float2 e = make_float2(keep_if_bit(ee.x, Ga.vis, 2 * j), keep_if_bit(ee.y, Ga.vis, 2 * j + 1));
-                l2 = add2(l2, e);
-                rs[2 * j] = __float_as_uint(e.x);
-                rs[2 * j + 1] = __float_as_uint(e.y);
-              }
-            }
-            tmem_st32(tcol, rs);
-            L += l2.x + l2.y;
-            tmem_st_wait();
-          }
-          tc_fence_before_sync();
-          warp_arrive(bars + B_ADONE + s, lane);
-          SBL_MARK(tr && t + 1 < 3, trb + 6 + 4 * (t + 1));
-        }
-        if (t >= 0) {
-          // B: D(t) = E - P (fp32, left by the tensor core) -> masked, packed bf16 into tensor memory, row sum
-          const int gg = gk + t, s = gg & 1;
-          mbar_wait(bars + B_PFULL + s, (gg >> 1) & 1, a.status, 36);
-          if (gg >= 1) mbar_wait(bars + B_DFREE, (gg - 1) & 1, a.status, 37);
-          tc_fence_after_sync();
-          SBL_MARK(tr && t < 3, trb + 7 + 4 * t);
+      // A: S(t) -> E = exp(tau S - pls) in place (fp32), row sum L
+      auto phase_a = [&](int t) {
+        const int gg = gk + t, s = gg & 1;
+        const Geo G = geometry(t);
+        mbar_wait(bars + B_SFULL + s, (gg >> 1) & 1, a.status, 35);
+        tc_fence_after_sync();
+        if (!G.none) {   // a chunk nobody sees is left as it is: B writes zeros for it
           const uint32_t tcol = lane_base + T_BUF + s * 128 + c0;
-          float2 d2 = make_float2(0.f, 0.f);
-          uint32_t dpk[16];
-          if (Gb.none) {
+          uint32_t rs[32];
+          tmem_ld32(tcol, rs);
+          tmem_ld_wait();
+          float2 l2 = make_float2(0.f, 0.f);
+          if (G.all) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) dpk[j] = 0u;
+            for (int j = 0; j < 16; ++j) {
+              const float2 x =
+                  fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
+              const float2 e = make_float2(ex2(x.x), ex2(x.y));
+              l2 = add2(l2, e);
+              rs[2 * j] = __float_as_uint(e.x);
+              rs[2 * j + 1] = __float_as_uint(e.y);
+            }
           } else {
-            uint32_t rp[32];
-            tmem_ld32(tcol, rp);
-            tmem_ld_wait();
-            if (Gb.all) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float2 d = make_float2(__uint_as_float(rp[2 * j]), __uint_as_float(rp[2 * j + 1]));
-                d2 = add2(d2, d);
-                dpk[j] = pack_bf16(d.x, d.y);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float2 d = make_float2(keep_if_bit(__uint_as_float(rp[2 * j]), Gb.vis, 2 * j),
-                                             keep_if_bit(__uint_as_float(rp[2 * j + 1]), Gb.vis, 2 * j + 1));
-                d2 = add2(d2, d);
-                dpk[j] = pack_bf16(d.x, d.y);
-              }
+            for (int j = 0; j < 16; ++j) {
+              const float2 x =
+                  fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
+              const float2 ee = make_float2(ex2(x.x), ex2(x.y));
+              const float2 e = make_float2(keep_if_bit(ee.x, G.vis, 2 * j), keep_if_bit(ee.y, G.vis, 2 * j + 1));
+              l2 = add2(l2, e);
+              rs[2 * j] = __float_as_uint(e.x);
+              rs[2 * j + 1] = __float_as_uint(e.y);
             }
           }
-          tmem_st16(lane_base + T_D + c0 / 2, dpk);
-          sd += d2.x + d2.y;
+          tmem_st32(tcol, rs);
+          L += l2.x + l2.y;
           tmem_st_wait();
-          tc_fence_before_sync();
-          warp_arrive(bars + B_BDONE + s, lane);
-          SBL_MARK(tr && t < 3, trb + 8 + 4 * t);
         }
-        Gb = Ga;
+        tc_fence_before_sync();
+        warp_arrive(bars + B_ADONE + s, lane);
+      };
+      // B: D(t) = E - P (fp32, left by the tensor core) -> masked, packed bf16 over the first 16 of this
+      // thread's own 32 columns, row sum
+      auto phase_b = [&](int t) {
+        const int gg = gk + t, s = gg & 1;
+        const Geo G = geometry(t);
+        mbar_wait(bars + B_PFULL + s, (gg >> 1) & 1, a.status, 36);
+        tc_fence_after_sync();
+        const uint32_t tcol = lane_base + T_BUF + s * 128 + c0;
+        float2 d2 = make_float2(0.f, 0.f);
+        uint32_t dpk[16];
+        if (G.none) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dpk[j] = 0u;
+        } else {
+          uint32_t rp[32];
+          tmem_ld32(tcol, rp);
+          tmem_ld_wait();
+          if (G.all) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float2 d = make_float2(__uint_as_float(rp[2 * j]), __uint_as_float(rp[2 * j + 1]));
+              d2 = add2(d2, d);
+              dpk[j] = pack_bf16(d.x, d.y);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float2 d = make_float2(keep_if_bit(__uint_as_float(rp[2 * j]), G.vis, 2 * j),
+                                           keep_if_bit(__uint_as_float(rp[2 * j + 1]), G.vis, 2 * j + 1));
+              d2 = add2(d2, d);
+              dpk[j] = pack_bf16(d.x, d.y);
+            }
+          }
+        }
+        tmem_st16(tcol, dpk);
+        sd += d2.x + d2.y;
+        tmem_st_wait();
+        tc_fence_before_sync();
+        warp_arrive(bars + B_BDONE + s, lane);
+      };
+      // first feature half of the next tile: its slot is free, its Q tile was loaded a tile ago
+      bool formed0 = !have_next;
+      auto form_next0 = [&]() {
+        const BandTile Tn = band_tile(a, cur_n);
+        prep_tile(it + 1, Tn, M_n, gq_n);
+        z_n = 0.f;
+        form_half(it + 1, 0, M_n, z_n);
+        formed0 = true;
+      };
+      // Two buffers: exponentials of two key tiles, then their packing, alternate; the features of the next
+      // query tile fill the time the tensor core needs for the last P products.
+      int ta = 0, tb2 = 0;
+      if (nt > 0) phase_a(0);
+      if (nt > 1) phase_a(1);
+      ta = nt < 2 ? nt : 2;
+      while (tb2 < nt) {
+        if (ta >= nt && !formed0) form_next0();
+        phase_b(tb2);
+        if (tb2 + 1 < nt) phase_b(tb2 + 1);
+        tb2 += 2;
+        if (ta < nt) phase_a(ta);
+        if (ta + 1 < nt) phase_a(ta + 1);
+        ta += 2;
       }
+      if (!formed0) form_next0();
+      if (have_next) form_half(it + 1, 1, M_n, z_n);
+      // A tile without key tiles passes no barrier that the other softmax warps take part in: order its
+      // exchange buffer writes behind their reads of the previous tile's
+      if (nt == 0 && !have_next) asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
       // ---- combine the column groups of each row ----
       // L + max(Z - dps, 1e-24) = max(Z + sum D, L + 1e-24), with sum D = L - dps
       s_xch[tid] = L;
-      s_xch[NSOFT + tid] = ((zp.x + zp.y) + (zm.x + zm.y)) + sd;
+      s_xch[NSOFT + tid] = z_c + sd;
       asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
       float ZD = 0.f;
       L = 0.f;
@@ -1219,16 +1326,20 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         ZD += s_xch[NSOFT + row + 128 * j];
       }
       // ---- epilogue: this thread writes 64/NCQ of the row's 64 outputs ----
-      SBL_MARK(tr, trb + 17);
       mbar_wait(bars + B_DONE, it & 1, a.status, 38);
       tc_fence_after_sync();
-      SBL_MARK(tr, trb + 18);
       const float inv = 1.f / fmaxf(ZD, L + 1e-24f);
+      // Nothing here is ever rescaled, so exponentials of very large logits (inputs an order of magnitude
+      // above unit-variance logits) leave the fp32 range: record that instead of returning inf / nan silently.
+      if (!(L < 1e30f) || !(fabsf(ZD) < 1e30f)) a.status[1] = 1;
       {
         // tensor-memory loads are warp-wide: every lane runs them
         uint32_t ro[16];
         tmem_ld16(lane_base + T_O + OW * cq, ro);
         tmem_ld_wait();
+        // O has been read: the next tile's first low-rank product may overwrite it
+        tc_fence_before_sync();
+        warp_arrive(bars + B_OFREE, lane);
         uint32_t o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -1236,22 +1347,24 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
         // Stage the 32 bytes of this thread in the V buffer (the tile's last O += D V has run), laid out as
         // the output tensor map expects: 128-byte rows, 16-byte chunks XORed with row % 8.  The producer
         // warp writes the tile out with one bulk store, which clips rows past the end of the sequence.
+        // (With key tiles, the V load this tile's products waited for was issued behind the previous tile's
+        // store; without any, wait for that store here.)
+        if (nt == 0 && it >= 1) mbar_wait(bars + B_OSTORED, (it - 1) & 1, a.status, 46);
         uint8_t* srow = smem + OFF_V + row * 128;
         *reinterpret_cast<uint4*>(srow + (((2 * cq) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<uint4*>(srow + (((2 * cq + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
         fence_async_smem();
         warp_arrive(bars + B_OFULL, lane);
       }
-      // O has been read: the next query tile's phi(Q) arrival (B_PHIQ) releases the low-rank MMA that overwrites it
-      SBL_MARK(tr, trb + 19);
+      M_c = M_n;
+      gq_c = gq_n;
+      z_c = z_n;
       gk += nt;
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  SBL_MARK(tid == 0, 71);
-  SBL_MARK_NS(tid == 0, 73);
-  if (warp == WP) {
+  if (warp == W_LOADKV) {
     __syncwarp();
     tmem_dealloc(tb, 512);
   }
@@ -1261,13 +1374,84 @@ __global__ void __launch_bounds__(band::NTHREADS) tc_band_kernel(const __grid_co
 // host side
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Encoded tensor maps are cached by what they describe: a forward issues eleven of them, and in a serving
+// loop over fixed buffers every one repeats.  Small, linear-probed, guarded by a mutex.
+struct TmapKey {
+  const void* base;
+  int rank;
+  uint64_t dims[4], strides[3];
+  uint32_t box[4];
+  bool operator==(const TmapKey& o) const {
+    if (base != o.base || rank != o.rank) return false;
+    for (int i = 0; i < rank; ++i)
+      if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+    for (int i = 0; i + 1 < rank; ++i)
+      if (strides[i] != o.strides[i]) return false;
+    return true;
+  }
+};
+struct TmapCache {
+  static constexpr int N = 64;
+  std::mutex mu;
+  TmapKey keys[N];
+  CUtensorMap maps[N];
+  int used = 0, next = 0;
+};
+TmapCache g_tmaps;
+
+bool cached_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                 const uint32_t* box) {
+  TmapKey k{};
+  k.base = base;
+  k.rank = rank;
+  for (int i = 0; i < rank; ++i) {
+    k.dims[i] = dims[i];
+    k.box[i] = box[i];
+    if (i + 1 < rank) k.strides[i] = strides[i];
+  }
+  std::lock_guard<std::mutex> lock(g_tmaps.mu);
+  for (int i = 0; i < g_tmaps.used; ++i)
+    if (g_tmaps.keys[i] == k) {
+      *out = g_tmaps.maps[i];
+      return true;
+    }
+  if (!encode_tmap_bf16(out, base, rank, dims, strides, box)) return false;
+  const int slot = g_tmaps.used < TmapCache::N ? g_tmaps.used++ : (g_tmaps.next++ % TmapCache::N);
+  g_tmaps.keys[slot] = k;
+  g_tmaps.maps[slot] = *out;
+  return true;
+}
+
 bool map_bthe(CUtensorMap* m, const void* base, int B, int rows, int H, int64_t sb, int64_t ss, int64_t sh,
               uint32_t box_rows) {
   const uint64_t dims[4] = {(uint64_t)kE, (uint64_t)rows, (uint64_t)H, (uint64_t)B};
   // a size-1 axis may carry any stride in torch; give the encoder a legal one
   const uint64_t str[3] = {(uint64_t)ss * 2, (uint64_t)(H > 1 ? sh : kE) * 2, (uint64_t)(B > 1 ? sb : kE) * 2};
   const uint32_t box[4] = {64, box_rows, 1, 1};
-  return encode_tmap_bf16(m, base, 4, dims, str, box);
+  return cached_tmap(m, base, 4, dims, str, box);
+}
+
+// Per-device facts that do not change: SM count, and that the kernels' shared-memory limit has been raised.
+struct DeviceInfo {
+  int sms = 0;
+  bool attr_keys[2] = {false, false};
+  bool attr_band = false;
+};
+std::mutex g_dev_mu;
+DeviceInfo g_dev[64];
+
+cudaError_t device_info(DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (d.sms == 0) {
+    if ((e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  }
+  *out = &d;
+  return cudaSuccess;
 }
 
 struct TcLayout {
@@ -1280,7 +1464,7 @@ struct TcLayout {
   int* status;
 };
 
-TcLayout tc_layout(const SblParams& p, const Workspace& ws, char* base) {
+TcLayout tc_layout(const Workspace& ws, char* base) {
   TcLayout l;
   l.wt32 = reinterpret_cast<float*>(base + ws.wt);
   l.wt16 = reinterpret_cast<__nv_bfloat16*>(base + ws.phiq);  // the tensor path has no phi(Q) section
@@ -1289,14 +1473,20 @@ TcLayout tc_layout(const SblParams& p, const Workspace& ws, char* base) {
   l.partial = reinterpret_cast<float*>(base + ws.partial);
   l.status = reinterpret_cast<int*>(base + ws.status);
   l.wmax = reinterpret_cast<float*>(base + ws.status + 16);
-  (void)p;
   return l;
+}
+
+bool map_phik(CUtensorMap* m, const __nv_bfloat16* phik, int S, int BH) {
+  const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)S, (uint64_t)BH};
+  const uint64_t str[2] = {(uint64_t)kM * 2, (uint64_t)S * kM * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  return cached_tmap(m, phik, 3, dims, str, box);
 }
 
 template <bool MAX_ONLY>
 cudaError_t launch_keys(const SblParams& p, const Workspace& ws, char* base, const float* beta_in, float* beta_out,
                         cudaStream_t st) {
-  const TcLayout l = tc_layout(p, ws, base);
+  const TcLayout l = tc_layout(ws, base);
   KeysArgs a{};
   if (!map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
       !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128))
@@ -1305,14 +1495,9 @@ cudaError_t launch_keys(const SblParams& p, const Workspace& ws, char* base, con
     const uint64_t dims[2] = {(uint64_t)kE, (uint64_t)kR};
     const uint64_t str[1] = {(uint64_t)kE * 2};
     const uint32_t box[2] = {64, 128};
-    if (!encode_tmap_bf16(&a.tm_w, l.wt16, 2, dims, str, box)) return cudaErrorInvalidValue;
+    if (!cached_tmap(&a.tm_w, l.wt16, 2, dims, str, box)) return cudaErrorInvalidValue;
   }
-  {
-    const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)p.S, (uint64_t)(p.B * p.H)};
-    const uint64_t str[2] = {(uint64_t)kM * 2, (uint64_t)p.S * kM * 2};
-    const uint32_t box[3] = {64, 128, 1};
-    if (!encode_tmap_bf16(&a.tm_phik, l.phik, 3, dims, str, box)) return cudaErrorInvalidValue;
-  }
+  if (!map_phik(&a.tm_phik, l.phik, p.S, p.B * p.H)) return cudaErrorInvalidValue;
   a.lengths = p.key_lengths;
   a.beta_in = beta_in;
   a.beta_out = beta_out;
@@ -1328,9 +1513,15 @@ cudaError_t launch_keys(const SblParams& p, const Workspace& ws, char* base, con
   a.S_total = p.S_total;
   a.tau = p.softmax_temp;
   a.half_log_m = (float)(log((double)kM) / 2.0);
-  cudaError_t e = cudaFuncSetAttribute(tc_keys_kernel<MAX_ONLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)keys::SMEM_BYTES);
+  DeviceInfo* dev = nullptr;
+  cudaError_t e = device_info(&dev);
   if (e != cudaSuccess) return e;
+  if (!dev->attr_keys[MAX_ONLY ? 1 : 0]) {
+    e = cudaFuncSetAttribute(tc_keys_kernel<MAX_ONLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)keys::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    dev->attr_keys[MAX_ONLY ? 1 : 0] = true;
+  }
   dim3 grid((unsigned)ws.nsplit, (unsigned)(p.B * p.H));
   tc_keys_kernel<MAX_ONLY><<<grid, keys::NTHREADS, keys::SMEM_BYTES, st>>>(a);
   return cudaGetLastError();
@@ -1358,7 +1549,7 @@ bool tc_supported(const SblParams& p) {
 
 cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char* base, cudaStream_t st,
                                   bool reset_status, float* beta_fill) {
-  const TcLayout l = tc_layout(p, ws, base);
+  const TcLayout l = tc_layout(ws, base);
   tc_prep_kernel<<<1, 1024, 0, st>>>(p.W, (float)sqrt((double)p.softmax_temp), l.wt32, l.wt16, p.r, p.E, l.status,
                                     l.wmax, reset_status ? 1 : 0, beta_fill, beta_fill ? p.B * p.H : 0);
   return cudaGetLastError();
@@ -1374,7 +1565,7 @@ cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base,
 
 cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st,
                                   bool beta_is_reset) {
-  const TcLayout l = tc_layout(p, ws, base);
+  const TcLayout l = tc_layout(ws, base);
   const int bh = p.B * p.H;
   if (!beta_is_reset) {
     tc_fill_kernel<<<(unsigned)div_up(bh, 256), 256, 0, st>>>(beta, -INFINITY, bh);
@@ -1396,7 +1587,7 @@ cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, 
   if (e != cudaSuccess) return e;
   const int bh = p.B * p.H;
   const int64_t n = (int64_t)bh * kM * (kPartialLd / 4);
-  const TcLayout l = tc_layout(p, ws, base);
+  const TcLayout l = tc_layout(ws, base);
   tc_combine_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(l.partial, ws.nsplit, bh, kv, ksum,
                                                              also_bf16 ? l.kv16 : nullptr);
   return cudaGetLastError();
@@ -1404,7 +1595,7 @@ cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, 
 
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta, const float* kv,
                     const float* ksum, cudaStream_t st, bool kv16_ready) {
-  const TcLayout l = tc_layout(p, ws, base);
+  const TcLayout l = tc_layout(ws, base);
   cudaError_t e = cudaSuccess;
   if (!kv16_ready) {
     const int64_t nkv = (int64_t)p.B * p.H * kM * kE;
@@ -1420,20 +1611,15 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   {
     const uint64_t dims[2] = {(uint64_t)kE, (uint64_t)kR};
     const uint64_t str[1] = {(uint64_t)kE * 2};
-    const uint32_t box[2] = {64, 128};
-    if (!encode_tmap_bf16(&a.tm_w, l.wt16, 2, dims, str, box)) return cudaErrorInvalidValue;
+    const uint32_t box[2] = {64, 64};      // one half of the projection rows per load
+    if (!cached_tmap(&a.tm_w, l.wt16, 2, dims, str, box)) return cudaErrorInvalidValue;
   }
-  {
-    const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)p.S, (uint64_t)(p.B * p.H)};
-    const uint64_t str[2] = {(uint64_t)kM * 2, (uint64_t)p.S * kM * 2};
-    const uint32_t box[3] = {64, 128, 1};
-    if (!encode_tmap_bf16(&a.tm_phik, l.phik, 3, dims, str, box)) return cudaErrorInvalidValue;
-  }
+  if (!map_phik(&a.tm_phik, l.phik, p.S, p.B * p.H)) return cudaErrorInvalidValue;
   {
     const uint64_t dims[3] = {(uint64_t)kE, (uint64_t)kM, (uint64_t)(p.B * p.H)};
     const uint64_t str[2] = {(uint64_t)kE * 2, (uint64_t)kM * kE * 2};
-    const uint32_t box[3] = {64, 256, 1};
-    if (!encode_tmap_bf16(&a.tm_kv, l.kv16, 3, dims, str, box)) return cudaErrorInvalidValue;
+    const uint32_t box[3] = {64, 128, 1};  // one feature half per load
+    if (!cached_tmap(&a.tm_kv, l.kv16, 3, dims, str, box)) return cudaErrorInvalidValue;
   }
   a.p = p;
   a.beta = beta;
@@ -1442,13 +1628,15 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
   a.status = l.status;
   a.ntq = (int)div_up(p.T, band::BQ);
   a.ntiles = a.ntq * p.B * p.H;
-  e = cudaFuncSetAttribute(tc_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band::SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  int dev = 0, sms = 0;
-  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
-  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  DeviceInfo* dev = nullptr;
+  if ((e = device_info(&dev)) != cudaSuccess) return e;
+  if (!dev->attr_band) {
+    e = cudaFuncSetAttribute(tc_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    dev->attr_band = true;
+  }
   // persistent: one CTA per SM (shared and tensor memory allow no more), each walking its share of the query tiles
-  const unsigned grid = (unsigned)(a.ntiles < sms ? a.ntiles : sms);
+  const unsigned grid = (unsigned)(a.ntiles < dev->sms ? a.ntiles : dev->sms);
   tc_band_kernel<<<grid, band::NTHREADS, band::SMEM_BYTES, st>>>(a);
   return cudaGetLastError();
 }
@@ -1459,11 +1647,11 @@ __global__ void tc_wait_selftest_kernel(int* status) {
   __shared__ uint64_t bar;
   if (threadIdx.x == 0) {
     *status = 0;
-    mbar_init(&bar, 1);
-    fence_mbar_init();
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_mbar_init();
   }
   __syncwarp();
-  mbar_wait(&bar, 0, status, 99);
+  ptx::mbar_wait(&bar, 0, status, 99);
 }
 
 cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t st) {
@@ -1475,15 +1663,9 @@ cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t 
 }
 
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st) {
-  cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, sizeof(int), cudaMemcpyDeviceToHost, st);
+  cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, 2 * sizeof(int), cudaMemcpyDeviceToHost, st);
   if (e != cudaSuccess) return e;
   return cudaStreamSynchronize(st);
 }
 
 }  // namespace sbl
-
-#ifdef SBL_TRACE
-extern "C" int sbl_trace_fetch(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, sbl::g_band_trace, sizeof(long long) * 160 * 96);
-}
-#endif

@@ -2,6 +2,7 @@
 launches on the current CUDA stream.  PyTorch is used only for device memory
 and streams; all arithmetic happens in libsblocal_b200.so.
 """
+import collections
 import ctypes
 import math
 import threading
@@ -13,6 +14,52 @@ from . import _cabi
 _DTYPES = {torch.float32: _cabi.SBL_DTYPE_F32, torch.bfloat16: _cabi.SBL_DTYPE_BF16}
 _ws_lock = threading.Lock()
 _workspaces = {}
+
+
+class _StatusWatch:
+    """Device status words of earlier forwards, looked at without ever blocking the host.
+
+    The tensor-core kernels leave two int32 words in the workspace (a bounded wait that ran out; an exponential
+    that left the fp32 range).  `post` queues an asynchronous copy of them into pinned host memory behind a
+    forward; `poll` inspects the copies that have already landed and raises for the first bad one.  A module
+    calls `poll` at the start of every forward, so a bad result is reported by the next call at the latest
+    (or by `Problem.check_status`, which synchronises)."""
+
+    def __init__(self):
+        self._lock = threading.Lock()
+        self._pending = collections.deque()
+        self._free = []
+
+    def post(self, workspace, offset, device):
+        with self._lock:
+            host = self._free.pop() if self._free else torch.empty(2, dtype=torch.int32).pin_memory()
+        words = workspace[offset:offset + 8].view(torch.int32)
+        host.copy_(words, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(device))
+        with self._lock:
+            self._pending.append((event, host))
+
+    def poll(self):
+        while True:
+            with self._lock:
+                if not self._pending or not self._pending[0][0].query():
+                    return
+                _, host = self._pending.popleft()
+                wait_site, out_of_range = host.tolist()
+                self._free.append(host)
+            if wait_site:
+                raise _cabi.SblError(_cabi.SBL_ERR_DEVICE_STATUS,
+                                     f'an earlier forward gave up on a bounded wait inside a kernel (wait site '
+                                     f'{wait_site}); its output is invalid')
+            if out_of_range:
+                raise _cabi.SblError(_cabi.SBL_ERR_DEVICE_STATUS,
+                                     'an earlier forward met logits beyond the range of the bf16 tensor-core kernels '
+                                     '(an exponential left the fp32 range); its output is invalid -- use fp32 inputs '
+                                     'or Problem(..., generic=True)')
+
+
+status_watch = _StatusWatch()
 
 
 class Problem:
@@ -79,6 +126,8 @@ class Problem:
         nbytes = ctypes.c_size_t(0)
         _cabi.check(lib.sbl_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
         self.workspace_bytes = nbytes.value
+        off = ctypes.c_size_t(0)
+        self.status_offset = off.value if lib.sbl_status_words(ctypes.byref(p), ctypes.byref(off)) == 0 else None
 
     def workspace(self):
         """Grow-only scratch buffer per (device, stream)."""
@@ -100,8 +149,12 @@ class Problem:
         return ws
 
     # -- entry points -----------------------------------------------------
-    def forward(self, workspace=None):
-        self._call(_cabi.load().sbl_forward, workspace=workspace)
+    def forward(self, workspace=None, watch=False):
+        """watch: queue a non-blocking copy of the kernels' status words (see `status_watch`)."""
+        ws = self._call(_cabi.load().sbl_forward, workspace=workspace)
+        if watch and self.status_offset is not None:
+            with torch.cuda.device(self.device):
+                status_watch.post(ws, self.status_offset, self.device)
         return self.out
 
     def check_status(self, workspace=None):
@@ -157,7 +210,8 @@ class Problem:
 
 
 def sblocal_forward(query, key, value, W, local_context, softmax_temp=None, softmax_eps=0.0,
-                    key_lengths=None, out=None):
+                    key_lengths=None, out=None, watch=False):
     """out (B,T,H,D) = SBLocal attention of query (B,T,H,E), key (B,S,H,E),
     value (B,S,H,D) with projection W (r,E); one call of `sbl_forward`."""
-    return Problem(query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths, out).forward()
+    return Problem(query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths,
+                   out).forward(watch=watch)

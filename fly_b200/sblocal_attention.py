@@ -19,7 +19,8 @@ from .feature_maps_sb import SBPerformerFeatures
 class _ForwardOnly(torch.autograd.Function):
     @staticmethod
     def forward(ctx, query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths):
-        return ops.sblocal_forward(query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths)
+        return ops.sblocal_forward(query, key, value, W, local_context, softmax_temp, softmax_eps, key_lengths,
+                                   watch=True)
 
     @staticmethod
     def backward(ctx, *grads):
@@ -56,6 +57,9 @@ class SBLocalAttention(nn.Module):
         """query (B,T,H,E), key (B,S,H,E), value (B,S,H,D); masks are mask
         objects (fly_b200.masking or the reference's).  Returns
         (out (B,T,H,D), None)."""
+        # A device-side problem of an earlier forward (a wait that ran out, logits beyond the bf16 kernels' range)
+        # surfaces here, without a host synchronisation: only status copies that have already landed are read.
+        ops.status_watch.poll()
         if self.causal:
             raise NotImplementedError('causal SBLocal attention is not built')
         if self.training and self.dropout.p > 0:
@@ -84,7 +88,7 @@ class SBLocalAttention(nn.Module):
         if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
             out = _ForwardOnly.apply(*args)
         else:
-            out = ops.sblocal_forward(*args)
+            out = ops.sblocal_forward(*args, watch=True)
         if out_dtype is not None:
             out = out.to(out_dtype)
         return out, None

@@ -10,7 +10,8 @@ src/models/attention/feature_maps_sb.py:78.
 
 Protocol per forward (rank g owns rows [lo, hi) of q, k, v, out):
   1. halo exchange: every rank sends the K/V rows other ranks' windows reach
-     into (point-to-point, into the receivers' own memory);
+     into (point-to-point, into the receivers' own memory); posted first and
+     waited for only after step 2 has been queued, which needs no halo row;
   2. sbl_key_logscale over the own rows        -> all-reduce MAX of (B,H) floats;
   3. sbl_key_summary over own rows (+phi(K) of the halo rows kept in the
      workspace)                                -> all-reduce SUM of (B,H,m,D+1) floats;
@@ -53,41 +54,62 @@ def plan_halo(bounds, w, rank):
     return sends, recvs
 
 
+class HaloExchange:
+    """Window-halo exchange in two steps, so that work which needs only the own rows can be queued in between.
+
+    start(): allocates the extended K/V buffers, copies the own rows in and posts the point-to-point transfers
+    (the landing buffers are this rank's own memory); finish(): waits for them and places the received rows."""
+
+    def __init__(self, k_local, v_local, bounds, w, group=None):
+        self.rank = dist.get_rank(group)
+        self.group = group
+        self.lo, self.hi = bounds[self.rank], bounds[self.rank + 1]
+        n_total = bounds[-1]
+        self.klo, self.khi = halo_range(self.lo, self.hi, w, n_total)
+        self.sends, self.recvs = plan_halo(bounds, w, self.rank)
+        self.k_local, self.v_local = k_local, v_local
+        self.k_ext = self.v_ext = None
+        self._reqs, self._landing, self._keep = [], [], []
+
+    def start(self):
+        k_local, v_local, lo, hi, klo, khi = self.k_local, self.v_local, self.lo, self.hi, self.klo, self.khi
+        B, _, H, E = k_local.shape
+        D = v_local.shape[-1]
+        self.k_ext = k_local.new_empty(B, khi - klo, H, E)
+        self.v_ext = v_local.new_empty(B, khi - klo, H, D)
+        self.k_ext[:, lo - klo:hi - klo] = k_local
+        self.v_ext[:, lo - klo:hi - klo] = v_local
+        ops_ = []
+        for peer, a, b in self.sends:
+            ks = k_local[:, a - lo:b - lo].contiguous()
+            vs = v_local[:, a - lo:b - lo].contiguous()
+            self._keep += [ks, vs]
+            ops_ += [dist.P2POp(dist.isend, ks, _global_rank(peer, self.group), self.group),
+                     dist.P2POp(dist.isend, vs, _global_rank(peer, self.group), self.group)]
+        for peer, a, b in self.recvs:
+            kr = k_local.new_empty(B, b - a, H, E)
+            vr = v_local.new_empty(B, b - a, H, D)
+            self._landing.append((a, b, kr, vr))
+            ops_ += [dist.P2POp(dist.irecv, kr, _global_rank(peer, self.group), self.group),
+                     dist.P2POp(dist.irecv, vr, _global_rank(peer, self.group), self.group)]
+        if ops_:
+            self._reqs = dist.batch_isend_irecv(ops_)
+        return self
+
+    def finish(self):
+        for req in self._reqs:
+            req.wait()
+        for a, b, kr, vr in self._landing:
+            self.k_ext[:, a - self.klo:b - self.klo] = kr
+            self.v_ext[:, a - self.klo:b - self.klo] = vr
+        self._reqs, self._keep = [], []
+        return self.k_ext, self.v_ext, self.klo
+
+
 def exchange_halo(k_local, v_local, bounds, w, group=None):
     """Returns (k_ext, v_ext, klo): the local K/V rows extended by the halo
     rows received from the neighbours, and the global position of row 0."""
-    rank = dist.get_rank(group)
-    lo, hi = bounds[rank], bounds[rank + 1]
-    n_total = bounds[-1]
-    klo, khi = halo_range(lo, hi, w, n_total)
-    sends, recvs = plan_halo(bounds, w, rank)
-    B, _, H, E = k_local.shape
-    D = v_local.shape[-1]
-    k_ext = k_local.new_empty(B, khi - klo, H, E)
-    v_ext = v_local.new_empty(B, khi - klo, H, D)
-    k_ext[:, lo - klo:hi - klo] = k_local
-    v_ext[:, lo - klo:hi - klo] = v_local
-    ops_, keep = [], []
-    for peer, a, b in sends:
-        ks = k_local[:, a - lo:b - lo].contiguous()
-        vs = v_local[:, a - lo:b - lo].contiguous()
-        keep += [ks, vs]
-        ops_ += [dist.P2POp(dist.isend, ks, _global_rank(peer, group), group),
-                 dist.P2POp(dist.isend, vs, _global_rank(peer, group), group)]
-    landing = []
-    for peer, a, b in recvs:
-        kr = k_local.new_empty(B, b - a, H, E)
-        vr = v_local.new_empty(B, b - a, H, D)
-        landing.append((a, b, kr, vr))
-        ops_ += [dist.P2POp(dist.irecv, kr, _global_rank(peer, group), group),
-                 dist.P2POp(dist.irecv, vr, _global_rank(peer, group), group)]
-    if ops_:
-        for req in dist.batch_isend_irecv(ops_):
-            req.wait()
-    for a, b, kr, vr in landing:
-        k_ext[:, a - klo:b - klo] = kr
-        v_ext[:, a - klo:b - klo] = vr
-    return k_ext, v_ext, klo
+    return HaloExchange(k_local, v_local, bounds, w, group).start().finish()
 
 
 def _global_rank(group_rank, group):
@@ -115,25 +137,45 @@ class CudaEngine:
 
 
 def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_total, softmax_temp=None,
-                             softmax_eps=0.0, key_lengths=None, group=None, engine_cls=CudaEngine):
+                             softmax_eps=0.0, key_lengths=None, group=None, engine_cls=CudaEngine, timings=None):
     """SBLocal forward of this rank's shard of one long sequence.
 
     q_local/k_local/v_local: (B, n_local, H, E|D), rows
     shard_bounds(n_total, world)[rank] ... [rank+1] of the full sequence.
     key_lengths: global (B,) key lengths or None.  Returns out (B, n_local, H, D).
+    timings: an empty list to be filled with (stage name, CUDA event) pairs recorded on the current stream
+    after each stage (CUDA ranks only).
     """
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     bounds = shard_bounds(n_total, world)
     lo, hi = bounds[rank], bounds[rank + 1]
     if q_local.shape[1] != hi - lo or k_local.shape[1] != hi - lo or v_local.shape[1] != hi - lo:
         raise ValueError(f'rank {rank} must hold rows [{lo},{hi}) of the sequence: got {q_local.shape[1]} rows')
-    k_ext, v_ext, klo = exchange_halo(k_local, v_local, bounds, int(local_context), group)
-    eng = engine_cls(q_local, k_ext, v_ext, W, int(local_context), softmax_temp, softmax_eps, key_lengths,
-                     lo, klo, n_total, hi - lo)
+    # The key log-scale reads the own rows only: it is queued while the halo rows are in flight, and its MAX
+    # all-reduce travels with them.  The summary and the band stage need the halo rows / the reduced summary.
+    mark = (lambda name: None) if timings is None else (lambda name: timings.append((name, _event())))
+    mark('start')
+    halo = HaloExchange(k_local, v_local, bounds, int(local_context), group).start()
+    eng = engine_cls(q_local, halo.k_ext, halo.v_ext, W, int(local_context), softmax_temp, softmax_eps, key_lengths,
+                     lo, halo.klo, n_total, hi - lo)
     beta = eng.key_logscale()
-    dist.all_reduce(beta, op=dist.ReduceOp.MAX, group=group)
+    mark('logscale')
+    beta_work = dist.all_reduce(beta, op=dist.ReduceOp.MAX, group=group, async_op=True)
+    halo.finish()
+    beta_work.wait()
+    mark('halo+max')
     kv, ksum = eng.key_summary(beta)
+    mark('summary')
     packed = torch.cat([kv, ksum.unsqueeze(-1)], dim=-1).contiguous()     # one collective for both
     dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
     kv, ksum = packed[..., :-1].contiguous(), packed[..., -1].contiguous()
-    return eng.band_forward(beta, kv, ksum)
+    mark('allreduce')
+    out = eng.band_forward(beta, kv, ksum)
+    mark('band')
+    return out
+
+
+def _event():
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    return ev

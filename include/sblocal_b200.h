@@ -145,11 +145,27 @@ int sbl_attention_weights(const SblParams* p, void* workspace, size_t workspace_
  * Synchronises the stream and reports whether any kernel of the preceding
  * calls on this workspace gave up on a bounded wait (every device-side wait
  * has an iteration limit, after which the kernel records the wait site,
- * finishes and frees its tensor memory): SBL_ERR_DEVICE_STATUS if so, and the
- * outputs of those calls are invalid.  No counterpart in the reference (its
- * device faults surface as CUDA errors).
+ * finishes and frees its tensor memory), or whether the bf16 tensor-core
+ * kernels met logits so large that an exponential left the fp32 range (those
+ * kernels never rescale; the generic kernels, SBL_FLAG_GENERIC_PATH, do):
+ * SBL_ERR_DEVICE_STATUS in both cases, and the outputs of those calls are
+ * invalid.  No counterpart in the reference (its device faults surface as
+ * CUDA errors, and its logsumexp form has no such range limit).
  */
 int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * For hosts that must not synchronise: *offset receives the byte offset, inside
+ * the workspace of this problem, of two int32 status words the tensor-core
+ * kernels write (word 0: site of a bounded wait that ran out, word 1: 1 if an
+ * exponential left the fp32 range because the logits are far above unit
+ * scale; both 0 = fine).  A caller may copy them out asynchronously behind a
+ * forward and look at them later; sbl_check_status reads the same words with
+ * a synchronisation.  Returns SBL_ERR_UNSUPPORTED for problems that run the
+ * generic kernels (they keep no status words).  No counterpart in the
+ * reference.
+ */
+int sbl_status_words(const SblParams* p, size_t* offset);
 
 /*
  * Self-test of that mechanism: launches one warp that waits on a barrier
@@ -179,14 +195,19 @@ int sbl_key_features(const SblParams* p, void* workspace, size_t workspace_bytes
  * No counterpart in the reference: an addition for hosts that are not allowed
  * to allocate device memory (a process whose GPU memory is owned by one
  * start-up arena, or a loop in which cudaMalloc is banned because it stalls
- * the device) and so cannot supply a workspace.  Same result as
- * sbl_key_logscale, but the scratch (sqrt(tau)*W, r*E floats) is a fixed
- * 128 KiB array inside the library image, present on every GPU that loads the
- * library.  Limits: r*E <= SBL_STATIC_PROJ_FLOATS, else SBL_ERR_UNSUPPORTED.
- * All calls on a device share that array; calls that overlap on the GPU race
- * on it, so keep them on one stream.  The first call on each device resolves
- * the array's address through the CUDA runtime: make it at start-up, before
- * any stream capture.  Allocates nothing.  Errors: sbl_static_last_error().
+ * the device) and so cannot supply a workspace.  Same value as
+ * sbl_key_logscale run with SBL_FLAG_GENERIC_PATH (the exact maximum, fp32
+ * projection); for bf16 inputs with E = 64, r = 128 the plain sbl_key_logscale
+ * takes the tensor-core kernels, which round the projection to bf16, and the
+ * two then differ by up to a few 1e-2 (both are valid stabilisers).  The
+ * scratch (sqrt(tau)*W, r*E floats) is a fixed 128 KiB array inside the
+ * library image, present on every GPU that loads the library.  Limits:
+ * r*E <= SBL_STATIC_PROJ_FLOATS, else SBL_ERR_UNSUPPORTED.  All calls on a
+ * device share that array; calls that overlap on the GPU race on it, so keep
+ * them on one stream.  The first call on each device resolves the array's
+ * address through the CUDA runtime, and the first launch per input dtype may
+ * load kernel code: make one call per dtype at start-up, before any stream
+ * capture.  Allocates nothing.  Errors: sbl_static_last_error().
  */
 #define SBL_STATIC_PROJ_FLOATS 32768
 int sbl_key_logscale_static(const SblParams* p, float* beta, void* cuda_stream);

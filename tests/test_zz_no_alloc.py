@@ -54,3 +54,31 @@ def test_static_scratch_rejects_oversized_projection(sbl_lib):
     rc, _ = _static_logscale(sbl_lib, prob)
     assert rc == _cabi.SBL_ERR_UNSUPPORTED
     assert b'exceeds' in sbl_lib.sbl_static_last_error()
+
+
+def test_static_scratch_on_the_tensor_core_shape(sbl_lib):
+    """bf16, E = 64, r = 128 is the one shape where `sbl_key_logscale` takes another route (tensor cores, on the
+    projection rounded to bf16) than the static call (fp32 projection, generic kernel): the two agree only to
+    bf16 accuracy there, and the static call agrees with the generic-path `sbl_key_logscale` exactly."""
+    from fly_b200 import ops
+    from oracle import sblocal_oracle as so
+    torch.manual_seed(12)
+    k = (torch.randn(2, 500, 2, 64, device='cuda') / 64 ** 0.25).bfloat16()
+    W = so.gaussian_orthogonal_random_matrix(128, 64).cuda()
+    for _ in range(2):                                     # two calls in a row share the array
+        rc, got = _static_logscale(sbl_lib, ops.Problem(k, k, k, W, 256))
+        assert rc == 0, sbl_lib.sbl_static_last_error().decode()
+        torch.cuda.synchronize()
+        generic = ops.Problem(k, k, k, W, 256, generic=True).key_logscale()
+        assert torch.allclose(got, generic, rtol=1e-5, atol=1e-5)
+        tensor = ops.Problem(k, k, k, W, 256).key_logscale()
+        assert torch.allclose(got, tensor, atol=5e-2)
+
+
+def test_static_scratch_checks_reserved_fields(sbl_lib):
+    from fly_b200 import ops, _cabi
+    k = torch.randn(1, 16, 1, 32, device='cuda')
+    prob = ops.Problem(k, k, k, torch.randn(8, 32, device='cuda'), 4)
+    prob.params.reserved[1] = 7
+    rc, _ = _static_logscale(sbl_lib, prob)
+    assert rc == _cabi.SBL_ERR_INVALID_ARGUMENT
