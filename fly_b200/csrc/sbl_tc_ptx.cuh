@@ -59,7 +59,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // *status and returns false.  The caller keeps going (its results are garbage,
 // but the kernel ends, frees its tensor memory and the host sees the status).
 constexpr uint32_t kWaitLimit = 1u << 18;   // about a second: an unsatisfied try_wait comes back after a few microseconds
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+// Not inlined on purpose: the kernels wait in dozens of places, and their instruction footprint matters more than
+// the call.
+static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(status) != 0) return false;

@@ -71,7 +71,7 @@ def key_features(k, W, tau, eps=0.0):
 
 
 def sblocal_forward(query, key, value, W, local_context, softmax_temp=None, softmax_eps=0.0,
-                    key_lengths=None, need_weights=False, row_chunk=512):
+                    key_lengths=None, need_weights=False, row_chunk=512, row_range=None):
     """src/models/attention/sblocal_attention.py:43-137 (non-causal, no
     attn_mask, dropout off).
 
@@ -79,6 +79,9 @@ def sblocal_forward(query, key, value, W, local_context, softmax_temp=None, soft
     (B,) or None.  Returns (out (B,T,H,D), extras) where extras is None or,
     with need_weights, the tuple the reference returns under
     return_attn_unnormalized=True (attn, attn*e^{log_norm}, attn'*e^{pls}).
+    row_range=(t0, t1): compute only those query rows (all keys still enter the
+    global summary); the other rows of `out` are left uninitialised.  For spot
+    checks of long sequences.
     """
     B, T, H, E = query.shape
     _, S, _, D = value.shape
@@ -104,8 +107,9 @@ def sblocal_forward(query, key, value, W, local_context, softmax_temp=None, soft
         attn = torch.zeros(B, H, T, S, dtype=dt)
         attn_un = torch.zeros(B, H, T, S, dtype=dt)
         attn_lr = torch.zeros(B, H, T, S, dtype=dt)
-    for t0 in range(0, T, row_chunk):
-        t1 = min(T, t0 + row_chunk)
+    r_lo, r_hi = (0, T) if row_range is None else row_range
+    for t0 in range(r_lo, r_hi, row_chunk):
+        t1 = min(r_hi, t0 + row_chunk)
         n = t1 - t0
         qc = q[:, :, t0:t1]
         q_prime, q_ls = query_features(qc, W, tau, softmax_eps)             # :78
