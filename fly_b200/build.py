@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, 'csrc')
 LIB_DIR = os.path.join(PKG, 'lib')
 LIB_PATH = os.path.join(LIB_DIR, 'libsblocal_b200.so')
 STAMP = os.path.join(LIB_DIR, 'libsblocal_b200.stamp')
-SOURCES = ['sbl_api.cu', 'sbl_f32.cu', 'sbl_tc.cu', 'sbl_tmap.cu', 'sbl_noalloc.cu']
+SOURCES = ['sbl_api.cu', 'sbl_f32.cu', 'sbl_tc.cu', 'sbl_tc128.cu', 'sbl_tmap.cu', 'sbl_noalloc.cu']
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
               '-Xcompiler', '-fPIC']
 

@@ -95,7 +95,9 @@ void plan_workspace(const SblParams& p, Workspace* ws) {
   if (ws->tensor) {
     // tensor path: CTAs stream 128-key tiles; about two CTAs per SM-count over all (b,h)
     const int ntiles = (int)div_up(p.S, 128);
-    int ns = (int)((296 + BH / 2) / BH);
+    // (head dim 128 runs four CTAs, one per projection quarter, on every split)
+    const size_t units = BH * (p.E == 128 ? 4 : 1);
+    int ns = (int)((296 + units / 2) / units);
     if (ns < 1) ns = 1;
     if (ns > ntiles) ns = ntiles;
     ws->nsplit = ns;
@@ -109,7 +111,7 @@ void plan_workspace(const SblParams& p, Workspace* ws) {
   ws->beta = off;    off = align_up(off + BH * 4);
   ws->kv = off;      off = align_up(off + BH * m * p.D * 4);
   ws->ksum = off;    off = align_up(off + BH * m * 4);
-  ws->partial = off; off = align_up(off + BH * ws->nsplit * m * (ws->tensor ? 80 : p.D + 1) * 4);
+  ws->partial = off; off = align_up(off + BH * ws->nsplit * m * (ws->tensor ? p.D + 16 : p.D + 1) * 4);
   ws->lognorm = off; off = align_up(off + (ws->tensor ? 0 : BH * p.T * 4));
   ws->status = off;  off = align_up(off + 64);
   ws->total = off;

@@ -2,7 +2,9 @@
 // tcgen05.mma with accumulators (and the phi(Q) / packed-weight operands) in
 // tensor memory, warp-specialised pipelines with mbarriers whose waits are
 // bounded.  Shapes: E = D = 64, r = 128 (m = 256), eps = 0, any T, S, w, key
-// lengths.  Everything else takes the generic kernels of sbl_f32.cu.
+// lengths (this file), and E = D = 128, r = 256 (m = 512), whose keys and band
+// kernels are in sbl_tc128.cu.  Everything else takes the generic kernels of
+// sbl_f32.cu.
 //
 // Kernels
 //   prep      sqrt(tau)*W -> bf16 (and fp32), clears the status words (and, for the fused forward, the log-scales)
@@ -41,83 +43,114 @@
 #include <mutex>
 
 #include "sbl_common.cuh"
-#include "sbl_tc_ptx.cuh"
+#include "sbl_tc_dev.cuh"
+#include "sbl_tc_host.cuh"
 
 namespace sbl {
+namespace tch {
+
+std::mutex g_dev_mu;
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Encoded tensor maps are cached by what they describe: a forward issues eleven of them, and in a serving
+// loop over fixed buffers every one repeats.  Small, linear-probed, guarded by a mutex.
+struct TmapKey {
+  const void* base;
+  int rank;
+  uint64_t dims[4], strides[3];
+  uint32_t box[4];
+  bool operator==(const TmapKey& o) const {
+    if (base != o.base || rank != o.rank) return false;
+    for (int i = 0; i < rank; ++i)
+      if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+    for (int i = 0; i + 1 < rank; ++i)
+      if (strides[i] != o.strides[i]) return false;
+    return true;
+  }
+};
+struct TmapCache {
+  static constexpr int N = 64;
+  std::mutex mu;
+  TmapKey keys[N];
+  CUtensorMap maps[N];
+  int used = 0, next = 0;
+};
+TmapCache g_tmaps;
+
+bool cached_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                 const uint32_t* box) {
+  TmapKey k{};
+  k.base = base;
+  k.rank = rank;
+  for (int i = 0; i < rank; ++i) {
+    k.dims[i] = dims[i];
+    k.box[i] = box[i];
+    if (i + 1 < rank) k.strides[i] = strides[i];
+  }
+  std::lock_guard<std::mutex> lock(g_tmaps.mu);
+  for (int i = 0; i < g_tmaps.used; ++i)
+    if (g_tmaps.keys[i] == k) {
+      *out = g_tmaps.maps[i];
+      return true;
+    }
+  if (!encode_tmap_bf16(out, base, rank, dims, strides, box)) return false;
+  const int slot = g_tmaps.used < TmapCache::N ? g_tmaps.used++ : (g_tmaps.next++ % TmapCache::N);
+  g_tmaps.keys[slot] = k;
+  g_tmaps.maps[slot] = *out;
+  return true;
+}
+
+bool map_bthe(CUtensorMap* m, const void* base, int B, int rows, int H, int E, int64_t sb, int64_t ss, int64_t sh,
+              uint32_t box_rows) {
+  const uint64_t dims[4] = {(uint64_t)E, (uint64_t)rows, (uint64_t)H, (uint64_t)B};
+  // a size-1 axis may carry any stride in torch; give the encoder a legal one
+  const uint64_t str[3] = {(uint64_t)ss * 2, (uint64_t)(H > 1 ? sh : E) * 2, (uint64_t)(B > 1 ? sb : E) * 2};
+  const uint32_t box[4] = {64, box_rows, 1, 1};
+  return cached_tmap(m, base, 4, dims, str, box);
+}
+
+
+DeviceInfo g_dev[64];
+
+cudaError_t device_info(DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (d.sms == 0) {
+    if ((e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  }
+  *out = &d;
+  return cudaSuccess;
+}
+
+
+TcLayout tc_layout(const Workspace& ws, char* base) {
+  TcLayout l;
+  l.wt32 = reinterpret_cast<float*>(base + ws.wt);
+  l.wt16 = reinterpret_cast<__nv_bfloat16*>(base + ws.phiq);  // the tensor path has no phi(Q) section
+  l.phik = reinterpret_cast<__nv_bfloat16*>(base + ws.phik);
+  l.kv16 = reinterpret_cast<__nv_bfloat16*>(base + ws.qls);   // nor query log-scales
+  l.partial = reinterpret_cast<float*>(base + ws.partial);
+  l.status = reinterpret_cast<int*>(base + ws.status);
+  l.wmax = reinterpret_cast<float*>(base + ws.status + 16);
+  return l;
+}
+
+}  // namespace tch
+
 namespace {
 
 using namespace ptx;
+using namespace tcdev;
+using namespace tch;
 
 constexpr int kE = 64;    // head dim (qk and v)
 constexpr int kR = 128;   // projection rows
 constexpr int kM = 256;   // features
-constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kPartialLd = 80;   // row pitch (floats) of a split-partial summary: 64 KV columns, the feature sum, padding
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
-
-__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
-  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
-  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
-}
-
-// Packed fp32 pairs (one issue slot for two lanes of arithmetic).
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "add.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-
-// One arrival for the whole warp, after every lane's earlier accesses are ordered before it.
-__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-}
-
-// v if bit k of mask is set, else 0 (two instructions: shift the bit into the sign, select on the sign)
-__device__ __forceinline__ float keep_if_bit(float v, uint32_t mask, int k) {
-  float d;
-  asm("slct.f32.s32 %0, %1, %2, %3;" : "=f"(d) : "f"(0.f), "f"(v), "r"((int)(mask << (31 - k))));
-  return d;
-}
-
-// sum of squares of one 64-element bf16 row held in a 128-byte swizzled line
-__device__ __forceinline__ float row_sumsq_sw128(const uint8_t* tile, int row) {
-  float s = 0.f;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const uint4 v = *reinterpret_cast<const uint4*>(tile + row * 128 + ((c ^ (row & 7)) << 4));
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float a = bf16_lo(w[j]), b = bf16_hi(w[j]);
-      s = fmaf(a, a, s);
-      s = fmaf(b, b, s);
-    }
-  }
-  return s;
-}
 
 // ---------------------------------------------------------------------------
 // One block of 1024 threads, 8 per projection row: sqrt(tau)*W in fp32 and bf16, the largest row
@@ -161,7 +194,8 @@ __global__ void __launch_bounds__(1024) tc_prep_kernel(const float* W, float c, 
 // +-u_f - tau|k|^2/2 - ln(m)/2 is at most wmax|k| - tau|k|^2/2 - ln(m)/2 (Cauchy-Schwarz, wmax = largest row norm
 // of the scaled projection).  With eps = 0 any stabiliser >= the true maximum gives the same output, so the
 // fused forward uses this one-pass, memory-bound bound instead of the exact maximum over all m features.
-// Eight lanes per key row (16 bytes each), 512 rows per block.
+// LPR lanes per key row (16 bytes each: LPR = E / 8), 16 * 256 / LPR rows per block.
+template <int LPR>
 __global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* k, int64_t sb, int64_t ss, int64_t sh,
                                                            int H, int row_lo, int row_hi, float tau, float half_log_m,
                                                            const float* wmax, float* beta) {
@@ -169,10 +203,11 @@ __global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* 
   const int bh = blockIdx.y, b = bh / H, h = bh % H;
   const __nv_bfloat16* base = k + b * sb + h * sh;
   const float wm = __ldg(wmax);
-  const int sub = threadIdx.x & 7;
+  constexpr int RPI = 256 / LPR;   // rows per iteration
+  const int sub = threadIdx.x % LPR;
   float best = -INFINITY;
   for (int it = 0; it < 16; ++it) {
-    const int row = row_lo + blockIdx.x * 512 + it * 32 + (threadIdx.x >> 3);
+    const int row = row_lo + blockIdx.x * (16 * RPI) + it * RPI + threadIdx.x / LPR;
     float s = 0.f;
     if (row < row_hi) {
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)row * ss) + sub);
@@ -184,9 +219,8 @@ __global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* 
         s = fmaf(y, y, s);
       }
     }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (row < row_hi) best = fmaxf(best, wm * sqrtf(s) - 0.5f * tau * s - half_log_m);
   }
 #pragma unroll
@@ -277,23 +311,6 @@ constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;    // + alignment slack
 constexpr uint32_t T_UK = 0;      // 2 x 128
 constexpr uint32_t T_KV = 256;    // 2 x 128 (80 used): [KV (64) | sum phi(K) (16 identical columns)] for feature blocks 0-127, 128-255
 }  // namespace keys
-
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem, int x, int y, int z) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(m)),
-               "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem, int x, int y, int z, int u) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(m)),
-               "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z), "r"(u)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <bool MAX_ONLY>
 __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_constant__ KeysArgs a) {
@@ -1392,110 +1409,6 @@ __global__ void __launch_bounds__(band::NTHREADS, 1) tc_band_kernel(const __grid
 
 // ---------------------------------------------------------------------------
 // host side
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-// Encoded tensor maps are cached by what they describe: a forward issues eleven of them, and in a serving
-// loop over fixed buffers every one repeats.  Small, linear-probed, guarded by a mutex.
-struct TmapKey {
-  const void* base;
-  int rank;
-  uint64_t dims[4], strides[3];
-  uint32_t box[4];
-  bool operator==(const TmapKey& o) const {
-    if (base != o.base || rank != o.rank) return false;
-    for (int i = 0; i < rank; ++i)
-      if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
-    for (int i = 0; i + 1 < rank; ++i)
-      if (strides[i] != o.strides[i]) return false;
-    return true;
-  }
-};
-struct TmapCache {
-  static constexpr int N = 64;
-  std::mutex mu;
-  TmapKey keys[N];
-  CUtensorMap maps[N];
-  int used = 0, next = 0;
-};
-TmapCache g_tmaps;
-
-bool cached_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                 const uint32_t* box) {
-  TmapKey k{};
-  k.base = base;
-  k.rank = rank;
-  for (int i = 0; i < rank; ++i) {
-    k.dims[i] = dims[i];
-    k.box[i] = box[i];
-    if (i + 1 < rank) k.strides[i] = strides[i];
-  }
-  std::lock_guard<std::mutex> lock(g_tmaps.mu);
-  for (int i = 0; i < g_tmaps.used; ++i)
-    if (g_tmaps.keys[i] == k) {
-      *out = g_tmaps.maps[i];
-      return true;
-    }
-  if (!encode_tmap_bf16(out, base, rank, dims, strides, box)) return false;
-  const int slot = g_tmaps.used < TmapCache::N ? g_tmaps.used++ : (g_tmaps.next++ % TmapCache::N);
-  g_tmaps.keys[slot] = k;
-  g_tmaps.maps[slot] = *out;
-  return true;
-}
-
-bool map_bthe(CUtensorMap* m, const void* base, int B, int rows, int H, int64_t sb, int64_t ss, int64_t sh,
-              uint32_t box_rows) {
-  const uint64_t dims[4] = {(uint64_t)kE, (uint64_t)rows, (uint64_t)H, (uint64_t)B};
-  // a size-1 axis may carry any stride in torch; give the encoder a legal one
-  const uint64_t str[3] = {(uint64_t)ss * 2, (uint64_t)(H > 1 ? sh : kE) * 2, (uint64_t)(B > 1 ? sb : kE) * 2};
-  const uint32_t box[4] = {64, box_rows, 1, 1};
-  return cached_tmap(m, base, 4, dims, str, box);
-}
-
-// Per-device facts that do not change: SM count, and that the kernels' shared-memory limit has been raised.
-struct DeviceInfo {
-  int sms = 0;
-  bool attr_keys[2] = {false, false};
-  bool attr_band = false;
-};
-std::mutex g_dev_mu;
-DeviceInfo g_dev[64];
-
-cudaError_t device_info(DeviceInfo** out) {
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  std::lock_guard<std::mutex> lock(g_dev_mu);
-  DeviceInfo& d = g_dev[dev];
-  if (d.sms == 0) {
-    if ((e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-  }
-  *out = &d;
-  return cudaSuccess;
-}
-
-struct TcLayout {
-  float* wmax;
-  __nv_bfloat16* wt16;
-  float* wt32;
-  __nv_bfloat16* phik;
-  __nv_bfloat16* kv16;
-  float* partial;
-  int* status;
-};
-
-TcLayout tc_layout(const Workspace& ws, char* base) {
-  TcLayout l;
-  l.wt32 = reinterpret_cast<float*>(base + ws.wt);
-  l.wt16 = reinterpret_cast<__nv_bfloat16*>(base + ws.phiq);  // the tensor path has no phi(Q) section
-  l.phik = reinterpret_cast<__nv_bfloat16*>(base + ws.phik);
-  l.kv16 = reinterpret_cast<__nv_bfloat16*>(base + ws.qls);   // nor query log-scales
-  l.partial = reinterpret_cast<float*>(base + ws.partial);
-  l.status = reinterpret_cast<int*>(base + ws.status);
-  l.wmax = reinterpret_cast<float*>(base + ws.status + 16);
-  return l;
-}
-
 bool map_phik(CUtensorMap* m, const __nv_bfloat16* phik, int S, int BH) {
   const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)S, (uint64_t)BH};
   const uint64_t str[2] = {(uint64_t)kM * 2, (uint64_t)S * kM * 2};
@@ -1508,8 +1421,8 @@ cudaError_t launch_keys(const SblParams& p, const Workspace& ws, char* base, con
                         cudaStream_t st) {
   const TcLayout l = tc_layout(ws, base);
   KeysArgs a{};
-  if (!map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
-      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128))
+  if (!map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, kE, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
+      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, kE, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128))
     return cudaErrorInvalidValue;
   {
     const uint64_t dims[2] = {(uint64_t)kE, (uint64_t)kR};
@@ -1555,13 +1468,14 @@ __global__ void tc_fill_kernel(float* p, float v, int n) {
 }  // namespace
 
 bool tc_supported(const SblParams& p) {
-  if (p.dtype != SBL_DTYPE_BF16 || p.E != kE || p.D != kE || p.r != kR) return false;
+  const bool shape64 = p.E == kE && p.D == kE && p.r == kR;
+  if (p.dtype != SBL_DTYPE_BF16 || !(shape64 || tc128_shape(p))) return false;
   if (p.softmax_eps != 0.f) return false;
   const int64_t strides[] = {p.q_stride_b, p.q_stride_t, p.q_stride_h, p.k_stride_b, p.k_stride_s, p.k_stride_h,
                              p.v_stride_b, p.v_stride_s, p.v_stride_h, p.o_stride_b, p.o_stride_t, p.o_stride_h};
   for (int64_t s : strides)
     if (s % 8 != 0 || s < 0) return false;
-  if (p.q_stride_t < kE || p.k_stride_s < kE || p.v_stride_s < kE || p.o_stride_t < kE) return false;
+  if (p.q_stride_t < p.E || p.k_stride_s < p.E || p.v_stride_s < p.E || p.o_stride_t < p.E) return false;
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.out)) return false;
   if (p.S_total >= (1ll << 30) || p.q_pos0 + p.T >= (1ll << 30)) return false;
   return true;
@@ -1576,6 +1490,8 @@ cudaError_t tc_prepare_projection(const SblParams& p, const Workspace& ws, char*
 }
 
 cudaError_t tc_key_logscale(const SblParams& p, const Workspace& ws, char* base, float* beta, cudaStream_t st) {
+  // head dim 128 has no exact-maximum pass: the one-pass bound is a valid stabiliser too (eps = 0)
+  if (tc128_shape(p)) return tc_key_logscale_bound(p, ws, base, beta, st, false);
   const int bh = p.B * p.H;
   tc_fill_kernel<<<(unsigned)div_up(bh, 256), 256, 0, st>>>(beta, -INFINITY, bh);
   cudaError_t e = cudaGetLastError();
@@ -1594,15 +1510,24 @@ cudaError_t tc_key_logscale_bound(const SblParams& p, const Workspace& ws, char*
   }
   const int rows = p.sum_hi - p.sum_lo;
   if (rows <= 0) return cudaSuccess;
-  dim3 grid((unsigned)div_up(rows, 512), (unsigned)bh);
-  tc_key_bound_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p.k), p.k_stride_b, p.k_stride_s,
-                                           p.k_stride_h, p.H, p.sum_lo, p.sum_hi, p.softmax_temp,
-                                           (float)(log((double)kM) / 2.0), l.wmax, beta);
+  const float half_log_m = (float)(log(2.0 * p.r) / 2.0);
+  if (p.E == 128) {
+    dim3 grid((unsigned)div_up(rows, 256), (unsigned)bh);
+    tc_key_bound_kernel<16><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p.k), p.k_stride_b,
+                                                 p.k_stride_s, p.k_stride_h, p.H, p.sum_lo, p.sum_hi, p.softmax_temp,
+                                                 half_log_m, l.wmax, beta);
+  } else {
+    dim3 grid((unsigned)div_up(rows, 512), (unsigned)bh);
+    tc_key_bound_kernel<8><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p.k), p.k_stride_b,
+                                                p.k_stride_s, p.k_stride_h, p.H, p.sum_lo, p.sum_hi, p.softmax_temp,
+                                                half_log_m, l.wmax, beta);
+  }
   return cudaGetLastError();
 }
 
 cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, const float* beta, float* kv,
                            float* ksum, cudaStream_t st, bool also_bf16) {
+  if (tc128_shape(p)) return tc128_key_summary(p, ws, base, beta, kv, ksum, st, also_bf16);
   cudaError_t e = launch_keys<false>(p, ws, base, beta, nullptr, st);
   if (e != cudaSuccess) return e;
   const int bh = p.B * p.H;
@@ -1615,6 +1540,7 @@ cudaError_t tc_key_summary(const SblParams& p, const Workspace& ws, char* base, 
 
 cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const float* beta, const float* kv,
                     const float* ksum, cudaStream_t st, bool kv16_ready) {
+  if (tc128_shape(p)) return tc128_band(p, ws, base, beta, kv, ksum, st, kv16_ready);
   const TcLayout l = tc_layout(ws, base);
   cudaError_t e = cudaSuccess;
   if (!kv16_ready) {
@@ -1623,10 +1549,10 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   BandArgs a{};
-  if (!map_bthe(&a.tm_q, p.q, p.B, p.T, p.H, p.q_stride_b, p.q_stride_t, p.q_stride_h, 128) ||
-      !map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
-      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128) ||
-      !map_bthe(&a.tm_out, p.out, p.B, p.T, p.H, p.o_stride_b, p.o_stride_t, p.o_stride_h, 128))
+  if (!map_bthe(&a.tm_q, p.q, p.B, p.T, p.H, kE, p.q_stride_b, p.q_stride_t, p.q_stride_h, 128) ||
+      !map_bthe(&a.tm_k, p.k, p.B, p.S, p.H, kE, p.k_stride_b, p.k_stride_s, p.k_stride_h, 128) ||
+      !map_bthe(&a.tm_v, p.v, p.B, p.S, p.H, kE, p.v_stride_b, p.v_stride_s, p.v_stride_h, 128) ||
+      !map_bthe(&a.tm_out, p.out, p.B, p.T, p.H, kE, p.o_stride_b, p.o_stride_t, p.o_stride_h, 128))
     return cudaErrorInvalidValue;
   {
     const uint64_t dims[2] = {(uint64_t)kE, (uint64_t)kR};

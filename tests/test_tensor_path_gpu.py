@@ -1,4 +1,4 @@
-"""The bf16 tensor-core kernels (E = D = 64, m = 256) against the CPU oracle
+"""The bf16 tensor-core kernels (E = D = 64, m = 256 and E = D = 128, m = 512) against the CPU oracle
 run in fp32 on the same bf16-rounded inputs.  Bound: max|out - ref| / max|ref|
 <= 2e-2.  Every call is followed by sbl_check_status, which fails if a
 device-side bounded wait ran out."""
@@ -11,15 +11,14 @@ pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
 
 
-def _inputs(B, T, S, H, seed, scale=None):
+def _inputs(B, T, S, H, seed, scale=None, E=64):
     g = torch.Generator().manual_seed(seed)
-    E = 64
     scale = scale or E ** 0.25
     q = (torch.randn(B, T, H, E, generator=g) / scale).bfloat16()
     k = (torch.randn(B, S, H, E, generator=g) / scale).bfloat16()
     v = (torch.randn(B, S, H, E, generator=g) / scale).bfloat16()
     torch.manual_seed(seed)
-    W = so.gaussian_orthogonal_random_matrix(128, E)
+    W = so.gaussian_orthogonal_random_matrix(2 * E, E)
     return q, k, v, W
 
 
@@ -264,3 +263,85 @@ def test_out_of_range_logits_are_reported(sbl_lib):
         ops.status_watch.poll()
     except _cabi.SblError:
         pass
+
+
+# ---- head dim 128, m = 512 (projection of 256 rows): the second shape of the tensor-core path ----
+
+def test_head_dim_128_takes_the_tensor_path(sbl_lib):
+    from fly_b200 import ops
+    q, k, v, W = _inputs(1, 256, 256, 1, seed=1, E=128)
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), 512)
+    assert pr.status_offset is not None      # only the tensor-core kernels keep status words
+
+
+@pytest.mark.parametrize('T,S,w', [(1100, 1100, 512), (640, 640, 512), (1000, 1000, 256), (130, 130, 512),
+                                   (777, 777, 33), (512, 512, 100), (300, 300, 257), (64, 64, 8), (500, 380, 128),
+                                   (380, 500, 128), (1, 1, 4), (2000, 2000, 1024)])
+def test_shapes_d128(T, S, w, sbl_lib):
+    q, k, v, W = _inputs(2, T, S, 2, seed=T + S + w, E=128)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
+    out = _run(q, k, v, W, w)
+    assert torch.isfinite(out).all()
+    assert so.rel_err(out, ref) <= TOL_BF16
+
+
+def test_ragged_lengths_d128(sbl_lib):
+    q, k, v, W = _inputs(4, 900, 900, 2, seed=9, E=128)
+    lengths = torch.tensor([900, 150, 611, 1])
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 512, None, 0.0, lengths)
+    assert so.rel_err(_run(q, k, v, W, 512, None, lengths), ref) <= TOL_BF16
+
+
+def test_summary_matches_oracle_d128(sbl_lib):
+    from fly_b200 import ops
+    q, k, v, W = _inputs(2, 900, 900, 2, seed=21, E=128)
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), 512)
+    beta = pr.key_logscale()
+    kv, ksum = pr.key_summary(beta)
+    pr.check_status()
+    kp, beta_ref = so.key_features(k.float().permute(0, 2, 1, 3), W, 128 ** -0.5)
+    # the library's beta is the one-pass bound from the key norms: any beta >= the maximum is a valid stabiliser
+    assert (beta.cpu() >= beta_ref.reshape(beta.shape) - 5e-2).all()
+    scale = torch.exp(beta_ref.reshape(2, 2) - beta.cpu())
+    kv_ref = torch.einsum('bhsm,bhsd->bhmd', kp, v.float().permute(0, 2, 1, 3)) * scale[..., None, None]
+    assert so.rel_err(kv.cpu(), kv_ref) < 1e-2
+    assert so.rel_err(ksum.cpu(), kp.sum(-2) * scale[..., None]) < 1e-2
+
+
+@pytest.mark.parametrize('chunks', [2, 3])
+def test_sequence_shards_on_one_gpu_d128(chunks, sbl_lib):
+    from fly_b200 import ops
+    q, k, v, W = _inputs(1, 1500, 1500, 2, seed=31, E=128)
+    w, N = 512, 1500
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
+    q, k, v, W = q.cuda(), k.cuda(), v.cuda(), W.cuda()
+    bounds = [N * i // chunks // 8 * 8 for i in range(chunks)] + [N]
+    probs = []
+    for g in range(chunks):
+        lo, hi = bounds[g], bounds[g + 1]
+        klo, khi = max(0, lo - w // 2), min(N, hi - 1 - w // 2 + w)
+        out = torch.empty(1, hi - lo, 2, 128, device='cuda', dtype=torch.bfloat16)
+        probs.append(ops.Problem(q[:, lo:hi], k[:, klo:khi], v[:, klo:khi], W, w, None, 0.0, None, out,
+                                 q_pos0=lo, k_pos0=klo, S_total=N, sum_range=(lo - klo, hi - klo)))
+    ws = [torch.empty(p.workspace_bytes, dtype=torch.uint8, device='cuda') for p in probs]
+    beta = torch.stack([p.key_logscale(workspace=x) for p, x in zip(probs, ws)]).amax(0)
+    parts = [p.key_summary(beta, workspace=x) for p, x in zip(probs, ws)]
+    kv = torch.stack([a for a, _ in parts]).sum(0)
+    ksum = torch.stack([b for _, b in parts]).sum(0)
+    outs = [p.band_forward(beta, kv, ksum, workspace=x) for p, x in zip(probs, ws)]
+    for p, x in zip(probs, ws):
+        p.check_status(workspace=x)
+    out = torch.cat(outs, dim=1).float().cpu()
+    assert so.rel_err(out, ref) <= TOL_BF16
+
+
+def test_long_sequence_d128_sampled_rows(sbl_lib):
+    """B1 H2 N = 16384 at the d = 128 / w = 512 / m = 512 head shape: whole output finite, and rows of three
+    windows (start, middle, end) against the oracle restricted to those rows."""
+    N, w = 16384, 512
+    q, k, v, W = _inputs(1, N, N, 2, seed=77, E=128)
+    out = _run(q, k, v, W, w)
+    assert torch.isfinite(out).all()
+    for t0 in (0, 8000, N - 300):
+        ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w, row_range=(t0, t0 + 300))
+        assert so.rel_err(out[:, t0:t0 + 300], ref[:, t0:t0 + 300]) <= TOL_BF16
