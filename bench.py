@@ -41,12 +41,14 @@ WORKLOADS = {
     'sblocal_bf16_B1_H8_N131072_d128_w512_m512': ('bf16', 1, 8, 131072, 128, 512, 512, 3),
     # a quarter of the default batch: small enough for a multi-pass ncu capture
     'sblocal_bf16_B2_H4_N16384_d64_w256_m256': ('bf16', 2, 4, 16384, 64, 256, 256, 2),
-    # the long sequence of the sharded configuration at the head shape the tensor-core kernels are built for
+    # the long sequence at the d = 64 head shape
     'sblocal_bf16_B1_H8_N131072_d64_w256_m256': ('bf16', 1, 8, 131072, 64, 256, 256, 3),
+    # one head of the long-sequence configuration: small enough for a multi-pass ncu capture
+    'sblocal_bf16_B1_H1_N131072_d128_w512_m512': ('bf16', 1, 1, 131072, 128, 512, 512, 3),
 }
 DEFAULT_WORKLOAD = 'sblocal_bf16_B2_H16_N16384_d64_w256_m256'
 CFG1_WORKLOAD = 'sblocal_fp32_B8_H1_N3136_d64_w256_m256'
-SEQSHARD_WORKLOAD = 'sblocal_bf16_B1_H8_N131072_d64_w256_m256'
+SEQSHARD_WORKLOAD = 'sblocal_bf16_B1_H8_N131072_d128_w512_m512'
 T2T_WORKLOAD = 't2t_vit_t14_b64'
 METRIC = 'sblocal_attn_fwd_tokens_per_s'
 
@@ -68,10 +70,11 @@ def load_band_traffic(B, H, N, d, w, m):
     if not os.path.exists(path):
         return None
     with open(path) as fh:
-        rec = json.load(fh)
-    if (rec['N'], rec['d'], rec['w'], rec['m']) != (N, d, w, m):
-        return None
-    return rec['dram_bytes_per_launch'] * (B * H) / rec['units']
+        records = json.load(fh)['records']
+    for rec in records:
+        if (rec['N'], rec['d'], rec['w'], rec['m']) == (N, d, w, m):
+            return rec['dram_bytes_per_launch'] * (B * H) / rec['units']
+    return None
 
 
 def flops_per_token_head(d, D, w, m):
@@ -360,7 +363,7 @@ def extra_seqshard(dev, rank, world, steps, barrier):
                               band=band_ms),
                 not_overlapped='the SUM all-reduce (every band tile needs the reduced summary) and what is left of '
                                'the halo wait after the key log-scale pass, which runs while the halo rows fly',
-                note='config 5 sequence length at the d=64/w=256/m=256 head shape of the tensor-core kernels')
+                note='the long-sequence configuration (d=128, w=512, m=512) through the tensor-core kernels')
 
 
 def run_t2t(args, dev):

@@ -443,23 +443,17 @@ static_assert(B_COUNT <= 32, "one phase bit per barrier");
 struct Tile128 {
   int bh, b, h, i0, nq, len_b, j0, nt;
 };
-struct Cursor128 {
-  int bh, qt;
-  __device__ Cursor128(const Band128Args& a, int tile_id) : bh(tile_id / a.ntq), qt(tile_id % a.ntq) {}
-  __device__ void next(const Band128Args& a) {
-    if (++qt == a.ntq) {
-      qt = 0;
-      ++bh;
-    }
-  }
-};
-__device__ __noinline__ Tile128 tile128(const Band128Args& a, const Cursor128& c) {
+// CTA c takes query tiles c, c + grid, c + 2 grid, ...: at any time the CTAs of the grid work on neighbouring
+// query tiles, so the K, V and phi(K) tiles that five neighbouring query tiles share are fetched from HBM once
+// and found in L2 by the other four (a CTA walking a contiguous run re-reads them long after L2 has lost them).
+__device__ __noinline__ Tile128 tile128(const Band128Args& a, int it) {
   const SblParams& p = a.p;
+  const int tile_id = blockIdx.x + it * gridDim.x;
   Tile128 t;
-  t.bh = c.bh;
+  t.bh = tile_id / a.ntq;
   t.b = t.bh / p.H;
   t.h = t.bh - t.b * p.H;
-  t.i0 = c.qt * band128::BQ;
+  t.i0 = (tile_id - t.bh * a.ntq) * band128::BQ;
   t.nq = min(band128::BQ, p.T - t.i0);
   t.len_b = (int)(p.key_lengths ? min(p.key_lengths[t.b], p.S_total) : p.S_total);
   const int hw = p.w / 2;
@@ -508,8 +502,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int hw = p.w / 2;
-  const int tile_lo = (int)((int64_t)a.ntiles * blockIdx.x / gridDim.x);
-  const int n_it = (int)((int64_t)a.ntiles * (blockIdx.x + 1) / gridDim.x) - tile_lo;
+  const int n_it = (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
   if (warp == W_MMA) {
     for (int i = lane; i < B_COUNT; i += 32) {
@@ -599,14 +592,12 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         }
       }
     };
-    Cursor128 cur(a, tile_lo);
-    Tile128 T = tile128(a, cur), Tn{};
+    Tile128 T = tile128(a, 0), Tn{};
     load_q(T);
 #pragma unroll 1
     for (int it = 0; it < n_it; ++it) {
-      cur.next(a);
       const bool have_next = it + 1 < n_it;
-      if (have_next) Tn = tile128(a, cur);
+      if (have_next) Tn = tile128(a, it + 1);
       const int nt = T.nt;
       load_w(0);
       for (int t = 0; t < min(nt, 2); ++t) load_rows(&a.tm_k, T, t);
@@ -710,10 +701,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       }
       __syncwarp();
     };
-    Cursor128 cur(a, tile_lo);
 #pragma unroll 1
-    for (int it = 0; it < n_it; ++it, cur.next(a)) {
-      const int nt = tile128(a, cur).nt;
+    for (int it = 0; it < n_it; ++it) {
+      const int nt = tile128(a, it).nt;
       ph.wait(bars, B_QFULL, a.status, 163);
       issue_qk(tb + T_PHI, bars + B_UFULL);
       for (int t = 0; t < min(nt, 2); ++t) issue_qk(tb + T_BUF + t * 128, bars + B_SFULL + t);
@@ -769,7 +759,6 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       return G;
     };
     Phases ph;
-    Cursor128 cur(a, tile_lo);
     if (exp_group) {
       const float wmax = __ldg(a.wmax);
       const float half_log_m = 0.5f * logf((float)kM);
@@ -814,8 +803,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         return zz.x + zz.y;
       };
 #pragma unroll 1
-      for (int it = 0; it < n_it; ++it, cur.next(a)) {
-        const Tile128 T = tile128(a, cur);
+      for (int it = 0; it < n_it; ++it) {
+        const Tile128 T = tile128(a, it);
         const int nt = T.nt;
         if (T.bh != bh_smem) {
           // every warp of the group is done with the old summary row before it is replaced
@@ -880,8 +869,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
     } else {
       RingPos rp;
 #pragma unroll 1
-      for (int it = 0; it < n_it; ++it, cur.next(a)) {
-        const Tile128 T = tile128(a, cur);
+      for (int it = 0; it < n_it; ++it) {
+        const Tile128 T = tile128(a, it);
         const int nt = T.nt;
         const int gi = (int)p.q_pos0 + T.i0 + row;
         float sd = 0.f;            // row sum of D over this thread's columns, both passes
