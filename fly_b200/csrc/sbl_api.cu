@@ -112,7 +112,7 @@ void plan_workspace(const SblParams& p, Workspace* ws) {
   ws->kv = off;      off = align_up(off + BH * m * p.D * 4);
   ws->ksum = off;    off = align_up(off + BH * m * 4);
   ws->partial = off; off = align_up(off + BH * ws->nsplit * m * (ws->tensor ? p.D + 16 : p.D + 1) * 4);
-  ws->lognorm = off; off = align_up(off + (ws->tensor ? 0 : BH * p.T * 4));
+  ws->lognorm = off; off = align_up(off + (ws->tensor ? BH * m * 4 : BH * p.T * 4));
   ws->status = off;  off = align_up(off + 64);
   ws->total = off;
 }

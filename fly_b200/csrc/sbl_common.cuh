@@ -23,7 +23,7 @@ struct Workspace {
   size_t kv;        // (B,H,m,D) fp32
   size_t ksum;      // (B,H,m) fp32
   size_t partial;   // split-S partial summaries
-  size_t lognorm;   // generic path: log_normalization per query row (B,H,T) fp32
+  size_t lognorm;   // generic: log_normalization per query row (B,H,T) fp32; tensor: sum phi(K) in the kernels' feature order (B,H,m)
   size_t status;    // int32[4] device status words, then small scalars
   size_t total;
   int nsplit;       // number of S splits of the summary GEMM

@@ -71,7 +71,7 @@ struct Phases {
 // kv (BH,512,128), ksum (BH,512) = sum over the splits of the per-CTA partial summaries.  The partials and
 // kv16 (the band kernel's bf16 operand) are in the internal feature order, kv and ksum in the reference's.
 __global__ void tc128_combine_kernel(const float* partial, int nsplit, int BH, float* kv, float* ksum,
-                                     __nv_bfloat16* kv16) {
+                                     __nv_bfloat16* kv16, float* ksum_slots) {
   constexpr int G = kPitch / 4;   // float4 groups per partial row: 32 of KV, then the feature sum
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (int64_t)BH * kM * G) return;
@@ -91,13 +91,16 @@ __global__ void tc128_combine_kernel(const float* partial, int nsplit, int BH, f
     if (kv16) *reinterpret_cast<uint2*>(kv16 + bf * kE + 4 * g) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
   } else {
     ksum[out_row] = acc.x;
+    if (kv16) ksum_slots[bf] = acc.x;   // the band kernel reads the feature sums in the internal order
   }
 }
 
 // kv (BH,512,128) fp32 in the reference's feature order -> bf16 in the internal order
-__global__ void tc128_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64_t n) {
+__global__ void tc128_kv_to_bf16_kernel(const float* kv, __nv_bfloat16* kv16, int64_t n, const float* ksum,
+                                        float* ksum_slots) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  if (i < n / kE) ksum_slots[i] = ksum[(i / kM) * kM + feat_of_slot((int)(i % kM))];
   const int d = (int)(i % kE);
   const int64_t row = i / kE;
   const int64_t bh = row / kM;
@@ -394,7 +397,7 @@ struct Band128Args {
   CUtensorMap tm_q, tm_k, tm_v, tm_w, tm_phik, tm_kv, tm_out;
   SblParams p;
   const float* beta;
-  const float* ksum;     // (BH, 512) fp32, reference feature order
+  const float* ksum;     // (BH, 512) fp32, internal feature order
   const float* wmax;     // [1]: max_f |sqrt(tau) w_f| of the bf16 projection
   int* status;
   int ntq;               // query tiles per (b,h)
@@ -410,10 +413,14 @@ constexpr int W_MMA = 17;                  // MMA issuer warp
 constexpr int NTHREADS = NSOFT + 64;
 constexpr uint32_t OFF_Q = 0;              // 32 KB: two blocks [128 q][64 e]
 constexpr uint32_t OFF_RING = 32768;       // ring of 32 KB slots: every B operand, and the staged output tile
-constexpr uint32_t NSLOT = 5, SLOT = 32768;
-constexpr uint32_t OFF_MISC = OFF_RING + NSLOT * SLOT;   // ksum fp32[512] | (L, Z) fp32[2][2][128] | sum D fp32[2][128]
-constexpr uint32_t OFF_BAR = OFF_MISC + 2048 + 2048 + 1024;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;
+// Six slots: with five, the refill of a slot (MMAs done -> load issued -> data landed) took a little longer than
+// the issuer needs for the five pieces in between, and every piece was waited for.  Six slots and the Q tile
+// leave 2.5 KB of the 227 KB: the feature sums are read from global memory (L1), the row sums of D are exchanged
+// through the output staging slot, and the kernel relies on (and checks) a 1024-byte aligned shared-memory base.
+constexpr uint32_t NSLOT = 6, SLOT = 32768;
+constexpr uint32_t OFF_MISC = OFF_RING + NSLOT * SLOT;   // (L, Z) fp32[2][2][128]
+constexpr uint32_t OFF_BAR = OFF_MISC + 2048;
+constexpr uint32_t SMEM_BYTES = OFF_BAR + 512;
 static_assert(SMEM_BYTES <= 232448, "dynamic shared memory of one CTA");
 // tensor memory columns (512)
 constexpr uint32_t T_O = 0;        // 128
@@ -491,13 +498,14 @@ struct RingPos {
 //   the output staging slot
 __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const __grid_constant__ Band128Args a) {
   using namespace band128;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled tiles need it; no slack is left to realign by hand
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, 142);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 62);
-  float* s_ksum = reinterpret_cast<float*>(smem + OFF_MISC);   // [512], internal feature order
-  float* s_lz = s_ksum + kM;        // [L, Z][2 column halves][128 rows]
-  float* s_sd = s_lz + 512;         // [2 column halves][128 rows]
+  float* s_lz = reinterpret_cast<float*>(smem + OFF_MISC);   // [L, Z][2 column halves][128 rows]
 
   const SblParams& p = a.p;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -599,6 +607,21 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       const bool have_next = it + 1 < n_it;
       if (have_next) Tn = tile128(a, it + 1);
       const int nt = T.nt;
+      // Pull the diagonal key tile of the NEXT query tile (K, V, phi(K): 192 KB) into L2 now.  The CTAs of the grid
+      // work on neighbouring query tiles, so between them they prefetch every key tile the grid's next round
+      // reads, and the ring loads of that round find their data in L2 instead of waiting for HBM.
+      if (have_next && leader) {
+        const int row0 = (int)(p.q_pos0 + Tn.i0 - p.k_pos0) / KT * KT;
+        if (row0 >= Tn.j0 && row0 < Tn.j0 + Tn.nt * KT) {
+#pragma unroll 1
+          for (int x = 0; x < kE; x += 64) {
+            tma_prefetch_4d(&a.tm_k, x, row0, Tn.h, Tn.b);
+            tma_prefetch_4d(&a.tm_v, x, row0, Tn.h, Tn.b);
+          }
+#pragma unroll 1
+          for (int x = 0; x < kM; x += 64) tma_prefetch_3d(&a.tm_phik, x, row0, Tn.bh);
+        }
+      }
       load_w(0);
       for (int t = 0; t < min(nt, 2); ++t) load_rows(&a.tm_k, T, t);
       load_kv(T, 0);
@@ -763,7 +786,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       const float wmax = __ldg(a.wmax);
       const float half_log_m = 0.5f * logf((float)kM);
       const float sc = p.softmax_temp * kLog2e;
-      int bh_smem = -1;
+      const float* ksum_bh = a.ksum;   // feature sums of the current (b,h), internal order
       float M = 0.f;
       // Features of one half, in place: this thread's 64 projections (four groups of 16 fp32 columns) become, per
       // group, 16 "+" and 16 "-" features (2 x 8 packed columns); returns its share of phi(Q) . sum phi(K).
@@ -778,7 +801,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         for (int g2 = 0; g2 < 4; ++g2) {
           const int c = 4 * cq + g2;               // group of 16 projections inside the half
           const uint32_t taddr = lane_base + T_PHI + 16 * c;
-          const float* ks = s_ksum + 256 * half + 32 * c;
+          const float* ks = ksum_bh + 256 * half + 32 * c;
           uint32_t r[16];
           tmem_ld16(taddr, r);
           tmem_ld_wait();
@@ -791,8 +814,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
             const float2 em = make_float2(ex2(am.x), ex2(am.y));
             p1[j] = pack_bf16(ep.x, ep.y);
             p2[j] = pack_bf16(em.x, em.y);
-            zz = fma2(ep, *reinterpret_cast<const float2*>(ks + 2 * j), zz);
-            zz = fma2(em, *reinterpret_cast<const float2*>(ks + 16 + 2 * j), zz);
+            zz = fma2(ep, __ldg(reinterpret_cast<const float2*>(ks + 2 * j)), zz);
+            zz = fma2(em, __ldg(reinterpret_cast<const float2*>(ks + 16 + 2 * j)), zz);
           }
           tmem_st8(taddr, p1);
           tmem_st8(taddr + 8, p2);
@@ -806,14 +829,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       for (int it = 0; it < n_it; ++it) {
         const Tile128 T = tile128(a, it);
         const int nt = T.nt;
-        if (T.bh != bh_smem) {
-          // every warp of the group is done with the old summary row before it is replaced
-          asm volatile("bar.sync 2, %0;" ::"n"(32 * WGRP) : "memory");
-          s_ksum[gtid] = __ldg(a.ksum + (int64_t)T.bh * kM + feat_of_slot(gtid));
-          s_ksum[gtid + 256] = __ldg(a.ksum + (int64_t)T.bh * kM + feat_of_slot(gtid + 256));
-          asm volatile("bar.sync 2, %0;" ::"n"(32 * WGRP) : "memory");
-          bh_smem = T.bh;
-        }
+        ksum_bh = a.ksum + (int64_t)T.bh * kM;
         // row norm, stabiliser M = wmax |q| >= |u_f| for every projection (Cauchy-Schwarz), key log-scale
         ph.wait(bars, B_QFULL, a.status, 171);
         const float qn2 = row_sumsq_sw128(smem + OFF_Q, row) + row_sumsq_sw128(smem + OFF_Q + 16384, row);
@@ -909,14 +925,22 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           tc_fence_before_sync();
           warp_arrive(bars + B_DDONE + s, lane);
         }
-        // ---- combine the column halves of each row ----
+        // this tile's staging slot: piece 6 + 7 nt of the tile
+        rp.advance(6 + 7 * nt);
+        const uint32_t oslot = rp.slot;
+        rp.advance();
+        ph.wait(bars, B_OUTREADY, a.status, 183);
+        // ---- combine the column halves of each row (the two threads of a row meet in the staging slot) ----
         // L + max(Z - dps, c) = max(Z + sum D, L + c), with sum D = L - dps
+        float* s_sd = reinterpret_cast<float*>(smem + OFF_RING + oslot * SLOT);   // [2 column halves][128 rows]
         s_sd[cq * 128 + row] = sd;
         asm volatile("bar.sync 3, %0;" ::"n"(32 * WGRP) : "memory");
         ph.wait(bars, B_LZFULL, a.status, 181);
         const float L = s_lz[row] + s_lz[128 + row];
         const float Zrow = s_lz[256 + row] + s_lz[384 + row];
         const float ZD = Zrow + (s_sd[row] + s_sd[128 + row]);
+        // every thread has read the exchange before any output line is staged over it
+        asm volatile("bar.sync 3, %0;" ::"n"(32 * WGRP) : "memory");
         ph.wait(bars, B_DONE, a.status, 182);
         tc_fence_after_sync();
         // The reference clamps Z - dps at 1e-24 in ITS feature units; ours are smaller by the slack of the bound
@@ -925,11 +949,6 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         // Nothing is ever rescaled: for inputs far above unit-variance logits the exponentials leave the fp32
         // range, or every feature of a row falls under it.  Record either instead of returning it silently.
         if (!(L < 1e30f) || !(fabsf(ZD) < 1e30f) || (Zrow == 0.f && T.len_b > 0)) a.status[1] = 1;
-        // this tile's staging slot: piece 6 + 7 nt of the tile
-        rp.advance(6 + 7 * nt);
-        const uint32_t oslot = rp.slot;
-        rp.advance();
-        ph.wait(bars, B_OUTREADY, a.status, 183);
         // This thread's 64 outputs = one 128-byte line of block cq of the staged tile, laid out as the output
         // tensor map expects: 16-byte chunks XORed with row % 8.
         uint8_t* srow = smem + OFF_RING + oslot * SLOT + cq * 16384 + row * 128;
@@ -975,6 +994,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
     tmem_dealloc(tb, 512);
   }
 }
+
+// feature sums in the internal order (the tensor path has no log-normalisation section)
+float* ksum_slots(const Workspace& ws, char* base) { return reinterpret_cast<float*>(base + ws.lognorm); }
 
 bool map_phik128(CUtensorMap* m, const __nv_bfloat16* phik, int S, int BH) {
   const uint64_t dims[3] = {(uint64_t)kM, (uint64_t)S, (uint64_t)BH};
@@ -1029,7 +1051,7 @@ cudaError_t tc128_key_summary(const SblParams& p, const Workspace& ws, char* bas
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   const int64_t n = (int64_t)bh * kM * (kPitch / 4);
   tc128_combine_kernel<<<(unsigned)div_up(n, 256), 256, 0, st>>>(l.partial, ws.nsplit, bh, kv, ksum,
-                                                                also_bf16 ? l.kv16 : nullptr);
+                                                                also_bf16 ? l.kv16 : nullptr, ksum_slots(ws, base));
   return cudaGetLastError();
 }
 
@@ -1039,7 +1061,7 @@ cudaError_t tc128_band(const SblParams& p, const Workspace& ws, char* base, cons
   cudaError_t e = cudaSuccess;
   if (!kv16_ready) {
     const int64_t nkv = (int64_t)p.B * p.H * kM * kE;
-    tc128_kv_to_bf16_kernel<<<(unsigned)div_up(nkv, 256), 256, 0, st>>>(kv, l.kv16, nkv);
+    tc128_kv_to_bf16_kernel<<<(unsigned)div_up(nkv, 256), 256, 0, st>>>(kv, l.kv16, nkv, ksum, ksum_slots(ws, base));
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   Band128Args a{};
@@ -1063,7 +1085,7 @@ cudaError_t tc128_band(const SblParams& p, const Workspace& ws, char* base, cons
   }
   a.p = p;
   a.beta = beta;
-  a.ksum = ksum;
+  a.ksum = ksum_slots(ws, base);
   a.wmax = l.wmax;
   a.status = l.status;
   a.ntq = (int)div_up(p.T, band128::BQ);

@@ -113,6 +113,12 @@ __device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* m, int x, int
                "r"(x), "r"(y), "r"(z), "r"(u)
                : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 
 // ---- tensor memory ---------------------------------------------------------------
 // Whole-warp calls.  ncols: power of two in [32, 512].
