@@ -73,7 +73,8 @@ class SBLocalAttention(nn.Module):
         W = self.feature_map.projection_matrix
         out_dtype = None
         if (self.compute_dtype == torch.bfloat16 and query.dtype == torch.float32 and not need_weights
-                and query.shape[-1] == 64 and value.shape[-1] == 64 and W.shape[0] == 128 and self.softmax_eps == 0):
+                and (query.shape[-1], value.shape[-1], W.shape[0]) in ((64, 64, 128), (128, 128, 256))
+                and self.softmax_eps == 0):
             out_dtype = query.dtype
             query, key, value = query.bfloat16(), key.bfloat16(), value.bfloat16()
         args = (query, key, value, W, self.local_context, self.softmax_temp, self.softmax_eps, key_lengths)

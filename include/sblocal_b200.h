@@ -104,6 +104,11 @@ int sbl_forward(const SblParams* p, void* workspace, size_t workspace_bytes, voi
  * features of (+-sqrt(tau) W k - tau|k|^2/2 - ln(m)/2): the key log-scale of
  * softmax_kernel(is_query=False) (src/models/attention/feature_maps_sb.py:77-78).
  * beta: (B,H) fp32 device.  Sequence-sharded callers all-reduce it with MAX.
+ * For bf16 inputs with E = D = 128, r = 256 and eps = 0 (the second shape of
+ * the tensor-core kernels) the value is an upper bound of that maximum taken
+ * from the key norms (wmax|k| - tau|k|^2/2 - ln(m)/2, wmax the largest row
+ * norm of sqrt(tau) W): with eps = 0 every stabiliser >= the maximum gives
+ * the same output, and stages 2 and 3 only need the SAME beta.
  */
 int sbl_key_logscale(const SblParams* p, void* workspace, size_t workspace_bytes, float* beta,
                      void* cuda_stream);
@@ -199,7 +204,8 @@ int sbl_key_features(const SblParams* p, void* workspace, size_t workspace_bytes
  * sbl_key_logscale run with SBL_FLAG_GENERIC_PATH (the exact maximum, fp32
  * projection); for bf16 inputs with E = 64, r = 128 the plain sbl_key_logscale
  * takes the tensor-core kernels, which round the projection to bf16, and the
- * two then differ by up to a few 1e-2 (both are valid stabilisers).  The
+ * two then differ by up to a few 1e-2 (both are valid stabilisers); with
+ * E = 128, r = 256 the plain call returns an upper bound from the key norms.  The
  * scratch (sqrt(tau)*W, r*E floats) is a fixed 128 KiB array inside the
  * library image, present on every GPU that loads the library.  Limits:
  * r*E <= SBL_STATIC_PROJ_FLOATS, else SBL_ERR_UNSUPPORTED.  All calls on a
