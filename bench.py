@@ -10,8 +10,10 @@ own (batch x head) units -- the path has no collective -- so the global batch
 is N times larger (weak scaling).  Rank 0 prints ONE JSON line.  The same line
 carries, under "extra":
   cfg1      the fp32 N=3136 configuration (second shape of the metric), 1 GPU only;
-  strong    N>1: the FIXED default batch split into contiguous (batch, head) ranges, 32/N units per rank;
-  seqshard  N>1: one long sequence (B1 H8 N131072) sharded along N: halo exchange + two all-reduces.
+  cfg3/cfg5 the bf16 B4 H12 N4096 d64 and B1 H8 N131072 d128 w512 m512 configurations, 1 GPU only;
+  strong    N>1: the FIXED default batch split into contiguous (batch, head) ranges, 32/N units per rank
+            (eager launches, and the same steps replayed from one CUDA graph);
+  seqshard  N>1: the long sequence (B1 H8 N131072 d128 w512 m512) sharded along N: halo exchange + two all-reduces.
 
 `--impl reference` times the reference's CPU forward on a bounded sample of the
 same workload: the reference module itself where its source tree can be
@@ -265,6 +267,28 @@ def extra_cfg1(dev, steps):
     return dict(workload=CFG1_WORKLOAD, dtype='f32', ms_per_step=ms_step, tokens_per_s=B * N / (ms_step * 1e-3),
                 tflops=flops / (ms_step * 1e-3) / 1e12, kernels='generic SIMT fp32 math',
                 l2='256 MB buffer rewritten between timed steps')
+
+
+def extra_tensor_config(dev, name, steps, peak_tf):
+    """Another bf16 configuration of the metric through the tensor-core kernels (inputs larger than L2, or the
+    256 MB flush between steps): time per forward and its fraction of the tensor roofline."""
+    from fly_b200 import ops
+    spec = WORKLOADS[name]
+    dtype, B, H, N, d, w, m, seed = spec
+    q, k, v, W = (t.to(dev) for t in make_inputs(spec, 'cpu'))
+    prob = ops.Problem(q, k, v, W, w)
+    step_bytes = 4 * B * H * N * d * 2
+    flush = None if step_bytes > 192e6 else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        prob.forward()
+    ms = timed_blocks(prob.forward, steps, 3, lambda: torch.cuda.synchronize(dev), flush)
+    prob.check_status()
+    ms_step = statistics.median(ms) / steps
+    tf = flops_per_token_head(d, d, w, m) * B * H * N / (ms_step * 1e-3) / 1e12
+    return dict(workload=name, dtype='bf16', ms_per_step=ms_step, tokens_per_s=B * N / (ms_step * 1e-3), tflops=tf,
+                roofline_frac=tf / peak_tf,
+                kernels='tcgen05+TMA bf16' if prob.status_offset is not None else 'generic SIMT fp32 math',
+                l2='inputs exceed L2' if flush is None else '256 MB buffer rewritten between timed steps')
 
 
 def extra_strong(dev, rank, world, spec, steps, barrier):
@@ -593,6 +617,10 @@ def main():
         if world == 1:
             if rank == 0:
                 extra['cfg1'] = extra_cfg1(dev, side_steps)
+                peak_tf = load_peaks()['bf16_tflops']
+                extra['cfg3'] = extra_tensor_config(dev, 'sblocal_bf16_B4_H12_N4096_d64_w256_m256', side_steps, peak_tf)
+                extra['cfg5'] = extra_tensor_config(dev, 'sblocal_bf16_B1_H8_N131072_d128_w512_m512', side_steps,
+                                                    peak_tf)
         else:
             extra['strong'] = extra_strong(dev, rank, world, spec, side_steps, barrier)
             extra['seqshard'] = extra_seqshard(dev, rank, world, side_steps, barrier)
