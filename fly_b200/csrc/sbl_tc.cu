@@ -350,12 +350,12 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(k_full + i, 1);
-      mbar_init(k_free + i, NFEAT);
+      mbar_init(k_free + i, NFEAT / 32);   // one arrival per feature warp
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(uk_full + i, 1);
-      mbar_init(uk_free + i, NFEAT);
-      mbar_init(a_full + i, NFEAT);
+      mbar_init(uk_free + i, NFEAT / 32);   // one arrival per feature warp
+      mbar_init(a_full + i, NFEAT / 32);   // one arrival per feature warp
       mbar_init(a_free + i, 2);
     }
     fence_mbar_init();
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
       const float g = 0.5f * a.tau * row_sumsq_sw128(smem + OFF_K + (i % KD) * 16384, krow);
       mbar_wait(uk_full + s, (i >> 1) & 1, a.status, 16);   // U computed: the tensor core is done with the K tile too
       tc_fence_after_sync();
-      mbar_arrive(k_free + (i % KD));
+      warp_arrive(k_free + (i % KD), lane);
       if (MAX_ONLY) {
         float mx = 0.f;
 #pragma unroll
@@ -504,7 +504,7 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         }
         if (row >= a.sum_lo && row < a.sum_hi) run_max = fmaxf(run_max, (mx - g) - a.half_log_m);
         tc_fence_before_sync();
-        mbar_arrive(uk_free + s);
+        warp_arrive(uk_free + s, lane);
       } else {
         const bool live = row < a.S && (a.k_pos0 + row) < len_b;
         const bool in_sum = live && row >= a.sum_lo && row < a.sum_hi;
@@ -554,8 +554,8 @@ __global__ void __launch_bounds__(keys::NTHREADS) tc_keys_kernel(const __grid_co
         }
         fence_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(a_full + s);
-        mbar_arrive(uk_free + s);
+        warp_arrive(a_full + s, lane);
+        warp_arrive(uk_free + s, lane);
       }
     }
     if (MAX_ONLY) {

@@ -10,7 +10,8 @@
 //             (N = 64), the feature warps write phi(K) in bf16 to the workspace
 //             and, MN-major, to shared memory, KV[128 f][128 d] += phi(K)^T V and
 //             sum phi(K) (a second product with a block of ones) accumulate in
-//             tensor memory; one partial summary per CTA.  The four quarter CTAs
+//             tensor memory; one partial summary per CTA (16 feature warps, 16
+//             projections per thread).  The four quarter CTAs
 //             of a split are neighbours in the grid, so the K and V tiles they
 //             all read meet in L2.
 //   combine128  sums the split partials -> KV (fp32 and bf16), sum phi(K)
@@ -124,7 +125,7 @@ struct Keys128Args {
 
 namespace keys128 {
 constexpr int TILE = 128;
-constexpr int NFEAT = 256;                 // feature threads: warp w owns key rows 32*(w%4).., 32 projections w/4
+constexpr int NFEAT = 512;                 // feature threads: warp w owns key rows 32*(w%4).., 16 projections w/4
 constexpr int WPK = NFEAT / 32;            // producer warp; WPK+1: MMA warp
 constexpr int NTHREADS = NFEAT + 64;
 constexpr uint32_t OFF_W = 0;                     // 16 KB: two blocks [64 r][64 e] (e 0-63, e 64-127) of this quarter of Wt
@@ -132,7 +133,8 @@ constexpr uint32_t OFF_K = 16384;                 // 2 x 32 KB: per key tile two
 constexpr uint32_t OFF_V = OFF_K + 65536;         // 2 x 32 KB: per key tile two blocks [128 keys][64 d] (MN-major, N = 128)
 constexpr uint32_t OFF_A = OFF_V + 65536;         // 2 x 32 KB: two blocks [128 keys][64 f] = phi(K) tile, MN-major A operand
 constexpr uint32_t OFF_ONES = OFF_A + 65536;      // 2 KB of bf16 ones: the B operand (N = 16) of the feature sum
-constexpr uint32_t OFF_BAR = OFF_ONES + 2048;
+constexpr uint32_t OFF_NORM = OFF_ONES + 2048;    // 4 KB: partial row norms, fp32 [2 tile parities][4 row quarters][128 keys]
+constexpr uint32_t OFF_BAR = OFF_NORM + 4096;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024;    // + alignment slack
 static_assert(SMEM_BYTES <= 232448, "dynamic shared memory of one CTA");
 // tensor memory columns
@@ -174,10 +176,10 @@ __global__ void __launch_bounds__(keys128::NTHREADS) tc128_keys_kernel(const __g
       mbar_init(v_full + i, 1);
       mbar_init(v_empty + i, 1);
       mbar_init(k_full + i, 1);
-      mbar_init(k_free + i, NFEAT);
+      mbar_init(k_free + i, NFEAT / 32);   // one arrival per feature warp
       mbar_init(uk_full + i, 1);
-      mbar_init(uk_free + i, NFEAT);
-      mbar_init(a_full + i, NFEAT);
+      mbar_init(uk_free + i, NFEAT / 32);   // one arrival per feature warp
+      mbar_init(a_full + i, NFEAT / 32);   // one arrival per feature warp
       mbar_init(a_free + i, 2);
     }
     fence_mbar_init();
@@ -300,33 +302,56 @@ __global__ void __launch_bounds__(keys128::NTHREADS) tc128_keys_kernel(const __g
     __syncwarp();
   } else {
     // ---------------- feature warps ----------------
-    const int qd = warp & 3, cq = warp >> 2;         // lane quarter (key rows), group of 32 projections
+    // Sixteen warps: with eight, a warp was busy 2.9 k cycles per tile (two warps per scheduler leave the latencies
+    // of the row-norm loads, the tensor-memory load and the exponentials exposed).
+    const int qd = warp & 3, cq = warp >> 2;         // lane quarter (key rows), group of 16 projections
     const int krow = qd * 32 + lane;                 // key row inside the tile
     const uint32_t lane_base = tb + ((uint32_t)(qd * 32) << 16);
     const float beta = a.beta[bh];
+    float* s_norm = reinterpret_cast<float*>(smem + OFF_NORM);
     for (int i = 0; i < nt; ++i) {
       const int s = i & 1;
       const int row = (t_lo + i) * TILE + krow;
       mbar_wait(k_full + s, (i >> 1) & 1, a.status, 118);
-      const uint8_t* kt = smem + OFF_K + s * 32768;
-      const float g = 0.5f * a.tau * (row_sumsq_sw128(kt, krow) + row_sumsq_sw128(kt + 16384, krow));
+      // |k|^2: each of the four threads of a row sums a quarter of it (64 bytes); they meet in shared memory behind
+      // a named barrier of their four warps.  The buffer alternates with the tile, so one barrier per tile does.
+      {
+        const uint8_t* line = smem + OFF_K + s * 32768 + (cq >> 1) * 16384 + krow * 128;
+        float part = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(line + (((4 * (cq & 1) + c) ^ (krow & 7)) << 4));
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x = bf16_lo(w4[j]), y = bf16_hi(w4[j]);
+            part = fmaf(x, x, part);
+            part = fmaf(y, y, part);
+          }
+        }
+        s_norm[(s * 4 + cq) * 128 + krow] = part;
+      }
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + qd) : "memory");
+      const float* nb = s_norm + s * 512 + krow;
+      const float g = 0.5f * a.tau * ((nb[0] + nb[128]) + (nb[256] + nb[384]));
       mbar_wait(uk_full + s, (i >> 1) & 1, a.status, 119);   // U computed: the tensor core is done with the K tile too
       tc_fence_after_sync();
-      mbar_arrive(k_free + s);
+      warp_arrive(k_free + s, lane);
       const bool live = row < a.S && (a.k_pos0 + row) < len_b;
       const bool in_sum = live && row >= a.sum_lo && row < a.sum_hi;
       const bool plain = tile_is_plain(i);
       const float off = ((-g - a.half_log_m) - beta) * kLog2e;
-      __nv_bfloat16* grow = a.phik + ((int64_t)bh * a.S + row) * kM + 128 * qt + 64 * cq;
-      uint8_t* sA = smem + OFF_A + s * 32768 + cq * 16384;
-      uint32_t r[32];
-      tmem_ld32(lane_base + T_UK + s * 64 + 32 * cq, r);
+      const int blk = cq >> 1, gi = cq & 1;            // 64-feature block, group of 16 projections inside it
+      __nv_bfloat16* grow = a.phik + ((int64_t)bh * a.S + row) * kM + 128 * qt + 64 * blk;
+      uint8_t* sA = smem + OFF_A + s * 32768 + blk * 16384;
+      uint32_t r[16];
+      tmem_ld16(lane_base + T_UK + s * 64 + 16 * cq, r);
       tmem_ld_wait();
       tc_fence_before_sync();
-      mbar_arrive(uk_free + s);
-      uint32_t p1[16], p2[16];
+      warp_arrive(uk_free + s, lane);
+      uint32_t p1[8], p2[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < 8; ++j) {
         constexpr float2 lp = {kLog2e, kLog2e}, lm = {-kLog2e, -kLog2e};
         const float2 u = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
         const float2 ap = fma2(u, lp, make_float2(off, off)), am = fma2(u, lm, make_float2(off, off));
@@ -335,38 +360,39 @@ __global__ void __launch_bounds__(keys128::NTHREADS) tc128_keys_kernel(const __g
         p1[j] = live ? pack_bf16(ep.x, ep.y) : 0u;
         p2[j] = live ? pack_bf16(em.x, em.y) : 0u;
       }
-      // The 32 projections fill one 64-feature block of the internal order: per group of 16 projections two
-      // 16-byte pieces of the "+" features, then two of the "-" features.
+      // A group of 16 projections fills half of a 64-feature block of the internal order: two 16-byte pieces of
+      // the "+" features, then two of the "-" features.
       if (!plain && row < a.S) {
 #pragma unroll
-        for (int q8 = 0; q8 < 8; ++q8) {
-          const uint32_t* src = ((q8 >> 1) & 1) ? p2 : p1;
-          const int o = 8 * (q8 >> 2) + 4 * (q8 & 1);
-          reinterpret_cast<uint4*>(grow)[q8] = make_uint4(src[o], src[o + 1], src[o + 2], src[o + 3]);
+        for (int x = 0; x < 4; ++x) {
+          const uint32_t* src = (x >> 1) ? p2 : p1;
+          const int o = 4 * (x & 1);
+          reinterpret_cast<uint4*>(grow)[4 * gi + x] = make_uint4(src[o], src[o + 1], src[o + 2], src[o + 3]);
         }
       }
       // the MMAs and the bulk store of the tile before the previous one must be done with the shared buffer
       if (i >= 2) mbar_wait(a_free + s, ((i >> 1) - 1) & 1, a.status, 120);
       // MN-major A operand: 16-byte piece q8 of the key's 128-byte line, swizzled by key % 8
 #pragma unroll
-      for (int q8 = 0; q8 < 8; ++q8) {
-        const uint32_t* src = ((q8 >> 1) & 1) ? p2 : p1;
-        const int o = 8 * (q8 >> 2) + 4 * (q8 & 1);
+      for (int x = 0; x < 4; ++x) {
+        const uint32_t* src = (x >> 1) ? p2 : p1;
+        const int o = 4 * (x & 1);
+        const int q8 = 4 * gi + x;
         const uint32_t so = (uint32_t)krow * 128u + (uint32_t)((q8 ^ (krow & 7)) << 4);
         *reinterpret_cast<uint4*>(sA + so) =
             in_sum ? make_uint4(src[o], src[o + 1], src[o + 2], src[o + 3]) : make_uint4(0, 0, 0, 0);
       }
       fence_async_smem();
-      mbar_arrive(a_full + s);
+      warp_arrive(a_full + s, lane);
     }
     mbar_wait(bar_done, 0, a.status, 121);
     tc_fence_after_sync();
-    // thread (feature row, half): writes 64 of the row's 128 KV columns; the second half also the feature sum
+    // thread (feature row, quarter): writes 32 of the row's 128 KV columns; the last quarter also the feature sum
     float* prow = a.partial + (((int64_t)bh * a.nsplit + split) * kM + 128 * qt + krow) * kPitch;
 #pragma unroll 1
-    for (int gq = 0; gq < 4; ++gq) {
+    for (int gq = 0; gq < 2; ++gq) {
       uint32_t r[16];
-      tmem_ld16(lane_base + T_KV + 64 * cq + 16 * gq, r);
+      tmem_ld16(lane_base + T_KV + 32 * cq + 16 * gq, r);
       tmem_ld_wait();
       if (nt == 0) {
 #pragma unroll
@@ -374,13 +400,13 @@ __global__ void __launch_bounds__(keys128::NTHREADS) tc128_keys_kernel(const __g
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        reinterpret_cast<uint4*>(prow + 64 * cq + 16 * gq)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        reinterpret_cast<uint4*>(prow + 32 * cq + 16 * gq)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
     }
     {
       uint32_t q[16];
       tmem_ld16(lane_base + T_KS, q);
       tmem_ld_wait();
-      if (cq == 1) prow[128] = nt == 0 ? 0.f : __uint_as_float(q[0]);
+      if (cq == 3) prow[128] = nt == 0 ? 0.f : __uint_as_float(q[0]);
     }
   }
   tc_fence_before_sync();
