@@ -267,7 +267,7 @@ int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes
     cudaError_t e = cudaStreamSynchronize(st);
     return e == cudaSuccess ? SBL_OK : cuda_fail(e, "stream synchronize");
   }
-  int host[2] = {0, 0};
+  int host[3] = {0, 0, 0};
   cudaError_t e = tc_read_status(ws, static_cast<char*>(workspace), host, st);
   if (e != cudaSuccess) return cuda_fail(e, "read device status");
   if (host[0] != 0)
@@ -277,6 +277,11 @@ int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes
     return fail(SBL_ERR_DEVICE_STATUS,
                 "numeric range: an exponential of the bf16 tensor-core kernels left the fp32 range (logits far above "
                 "unit scale); results are invalid -- rerun with SBL_FLAG_GENERIC_PATH");
+  if (host[2] != 0)
+    return fail(SBL_ERR_DEVICE_STATUS,
+                "precision: for some query rows the in-window low-rank estimate is more than 16 times the exact "
+                "in-window softmax mass (logits 3-4 times the unit scale), where the bf16 tensor-core kernels lose "
+                "accuracy (row error ~ that ratio x 2^-8); rerun with SBL_FLAG_GENERIC_PATH");
   return SBL_OK;
 }
 

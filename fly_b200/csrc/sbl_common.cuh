@@ -70,8 +70,9 @@ cudaError_t tc_band(const SblParams& p, const Workspace& ws, char* base, const f
                     const float* kv, const float* ksum, cudaStream_t st, bool kv16_ready = false);
 // runs a kernel whose only wait can never be satisfied; *host_status receives the recorded wait site (99)
 cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t st);
-// copies the two device status words (host_status[0]: wait site that ran out, host_status[1]: 1 if an
-// exponential left the fp32 range) and synchronises the stream
+// copies the three device status words (host_status[0]: wait site that ran out, host_status[1]: 1 if an
+// exponential left the fp32 range, host_status[2]: 1 if a row's low-rank estimate swamped its exact part) and
+// synchronises the stream
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st);
 
 }  // namespace sbl

@@ -206,22 +206,32 @@ __global__ void __launch_bounds__(256) tc_key_bound_kernel(const __nv_bfloat16* 
   constexpr int RPI = 256 / LPR;   // rows per iteration
   const int sub = threadIdx.x % LPR;
   float best = -INFINITY;
-  for (int it = 0; it < 16; ++it) {
-    const int row = row_lo + blockIdx.x * (16 * RPI) + it * RPI + threadIdx.x / LPR;
-    float s = 0.f;
-    if (row < row_hi) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)row * ss) + sub);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  // four rows per thread in flight at a time: the pass is a pure stream over K and one load per thread and
+  // iteration leaves it latency-bound
+#pragma unroll 1
+  for (int it = 0; it < 16; it += 4) {
+    uint4 v[4];
+    int rows[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      rows[u] = row_lo + blockIdx.x * (16 * RPI) + (it + u) * RPI + threadIdx.x / LPR;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (rows[u] < row_hi) v[u] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)rows[u] * ss) + sub);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      float s = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float x = bf16_lo(w[j]), y = bf16_hi(w[j]);
         s = fmaf(x, x, s);
         s = fmaf(y, y, s);
       }
-    }
 #pragma unroll
-    for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (row < row_hi) best = fmaxf(best, wm * sqrtf(s) - 0.5f * tau * s - half_log_m);
+      for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (rows[u] < row_hi) best = fmaxf(best, wm * sqrtf(s) - 0.5f * tau * s - half_log_m);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -1369,6 +1379,10 @@ __global__ void __launch_bounds__(band::NTHREADS, 1) tc_band_kernel(const __grid
         // fp32 range (queries and keys ~15 times the unit scale), or every feature of a row falls under it (the
         // bound stabilisers' slack grows with the norms): record either instead of returning it silently.
         if (!(L < 1e30f) || !(fabsf(ZD) < 1e30f) || (Zrow == 0.f && T.len_b > 0)) a.status[1] = 1;
+        // Precision, not range: where the in-window low-rank estimate (dps = L - sum D) is more than 16 times the exact
+        // in-window mass L, D = E - P is a small difference of large bf16-rounded terms and the row's error is about
+        // that ratio times 2^-8 (inputs 3-4 times the unit logit scale do this to a few rows).  Report it.
+        if (ZD - Zrow < -15.f * L) a.status[2] = 1;
         {
           // tensor-memory loads are warp-wide: every lane runs them
           uint32_t ro[32];
@@ -1609,7 +1623,7 @@ cudaError_t tc_wait_selftest(int* device_status, int* host_status, cudaStream_t 
 }
 
 cudaError_t tc_read_status(const Workspace& ws, char* base, int* host_status, cudaStream_t st) {
-  cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, 2 * sizeof(int), cudaMemcpyDeviceToHost, st);
+  cudaError_t e = cudaMemcpyAsync(host_status, base + ws.status, 3 * sizeof(int), cudaMemcpyDeviceToHost, st);
   if (e != cudaSuccess) return e;
   return cudaStreamSynchronize(st);
 }

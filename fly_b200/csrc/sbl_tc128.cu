@@ -975,6 +975,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         // Nothing is ever rescaled: for inputs far above unit-variance logits the exponentials leave the fp32
         // range, or every feature of a row falls under it.  Record either instead of returning it silently.
         if (!(L < 1e30f) || !(fabsf(ZD) < 1e30f) || (Zrow == 0.f && T.len_b > 0)) a.status[1] = 1;
+        // Precision: the in-window low-rank estimate (dps = L - sum D) more than 16 times the exact in-window mass L makes
+        // D a small difference of large bf16-rounded terms; the row's error is about that ratio times 2^-8.
+        if (ZD - Zrow < -15.f * L) a.status[2] = 1;
         // This thread's 64 outputs = one 128-byte line of block cq of the staged tile, laid out as the output
         // tensor map expects: 16-byte chunks XORed with row % 8.
         uint8_t* srow = smem + OFF_RING + oslot * SLOT + cq * 16384 + row * 128;

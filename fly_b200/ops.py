@@ -19,8 +19,8 @@ _workspaces = {}
 class _StatusWatch:
     """Device status words of earlier forwards, looked at without ever blocking the host.
 
-    The tensor-core kernels leave two int32 words in the workspace (a bounded wait that ran out; an exponential
-    that left the fp32 range).  `post` queues an asynchronous copy of them into pinned host memory behind a
+    The tensor-core kernels leave three int32 words in the workspace (a bounded wait that ran out; an exponential
+    that left the fp32 range; a row whose low-rank estimate swamped its exact part).  `post` queues an asynchronous copy of them into pinned host memory behind a
     forward; `poll` inspects the copies that have already landed and raises for the first bad one.  A module
     calls `poll` at the start of every forward, so a bad result is reported by the next call at the latest
     (or by `Problem.check_status`, which synchronises)."""
@@ -32,8 +32,8 @@ class _StatusWatch:
 
     def post(self, workspace, offset, device):
         with self._lock:
-            host = self._free.pop() if self._free else torch.empty(2, dtype=torch.int32).pin_memory()
-        words = workspace[offset:offset + 8].view(torch.int32)
+            host = self._free.pop() if self._free else torch.empty(3, dtype=torch.int32).pin_memory()
+        words = workspace[offset:offset + 12].view(torch.int32)
         host.copy_(words, non_blocking=True)
         event = torch.cuda.Event()
         event.record(torch.cuda.current_stream(device))
@@ -46,7 +46,7 @@ class _StatusWatch:
                 if not self._pending or not self._pending[0][0].query():
                     return
                 _, host = self._pending.popleft()
-                wait_site, out_of_range = host.tolist()
+                wait_site, out_of_range, imprecise = host.tolist()
                 self._free.append(host)
             if wait_site:
                 raise _cabi.SblError(_cabi.SBL_ERR_DEVICE_STATUS,
@@ -57,6 +57,12 @@ class _StatusWatch:
                                      'an earlier forward met logits beyond the range of the bf16 tensor-core kernels '
                                      '(an exponential left the fp32 range); its output is invalid -- use fp32 inputs '
                                      'or Problem(..., generic=True)')
+            if imprecise:
+                raise _cabi.SblError(_cabi.SBL_ERR_DEVICE_STATUS,
+                                     'an earlier forward met query rows whose in-window low-rank estimate is more than '
+                                     '16 times their exact softmax mass (logits 3-4 times the unit scale): the bf16 '
+                                     'tensor-core kernels lose accuracy there -- use fp32 inputs or '
+                                     'Problem(..., generic=True)')
 
 
 status_watch = _StatusWatch()

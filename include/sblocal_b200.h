@@ -152,19 +152,23 @@ int sbl_attention_weights(const SblParams* p, void* workspace, size_t workspace_
  * has an iteration limit, after which the kernel records the wait site,
  * finishes and frees its tensor memory), or whether the bf16 tensor-core
  * kernels met logits so large that an exponential left the fp32 range (those
- * kernels never rescale; the generic kernels, SBL_FLAG_GENERIC_PATH, do):
- * SBL_ERR_DEVICE_STATUS in both cases, and the outputs of those calls are
- * invalid.  No counterpart in the reference (its device faults surface as
+ * kernels never rescale; the generic kernels, SBL_FLAG_GENERIC_PATH, do), or
+ * met query rows whose in-window low-rank estimate is more than 16 times their
+ * exact in-window softmax mass, where bf16 products lose accuracy (row error
+ * about that ratio times 2^-8; logits 3-4 times the unit scale do this):
+ * SBL_ERR_DEVICE_STATUS in all three cases; the outputs of those calls are
+ * invalid in the first two and degraded in the third.  No counterpart in the reference (its device faults surface as
  * CUDA errors, and its logsumexp form has no such range limit).
  */
 int sbl_check_status(const SblParams* p, void* workspace, size_t workspace_bytes, void* cuda_stream);
 
 /*
  * For hosts that must not synchronise: *offset receives the byte offset, inside
- * the workspace of this problem, of two int32 status words the tensor-core
+ * the workspace of this problem, of three int32 status words the tensor-core
  * kernels write (word 0: site of a bounded wait that ran out, word 1: 1 if an
  * exponential left the fp32 range because the logits are far above unit
- * scale; both 0 = fine).  A caller may copy them out asynchronously behind a
+ * scale, word 2: 1 if a row's low-rank estimate swamped its exact part, see
+ * sbl_check_status; all 0 = fine).  A caller may copy them out asynchronously behind a
  * forward and look at them later; sbl_check_status reads the same words with
  * a synchronisation.  Returns SBL_ERR_UNSUPPORTED for problems that run the
  * generic kernels (they keep no status words).  No counterpart in the

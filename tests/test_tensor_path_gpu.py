@@ -209,15 +209,16 @@ def test_benchmark_shapes_against_oracle(name, B, H, N, seed, sbl_lib):
         assert so.rel_err(out[b:b + 1, :, h:h + 1], ref) <= TOL_BF16
 
 
-@pytest.mark.parametrize('factor,bound', [(2.0, TOL_BF16), (4.0, 0.1), (6.0, 0.1)])
-def test_scaled_inputs(factor, bound, sbl_lib):
+@pytest.mark.parametrize('factor,expect', [(2.0, 'ok'), (4.0, 'precision'), (6.0, 'ok')])
+def test_scaled_inputs(factor, expect, sbl_lib):
     """Queries and keys `factor` times the benchmark scale (logits factor^2 times larger).  Up to twice the scale
-    the tensor-core kernels stay inside the bf16 bound.  Beyond it their accuracy degrades before their range ends:
-    the low-rank estimate of such peaked logits consists of a few huge, mutually cancelling terms, and features,
-    KV and D = E - P rounded to bf16 leave errors relative to those terms (measured: 9e-2 at 4x, 6e-3 at 6x, where
-    the exact part dominates again).  The kernels never rescale an accumulator, so their range is finite too: past
-    it the call reports the numeric range (next test).  Here: finite output within the stated loose bound, or a
-    report -- and the fp32-math kernels within the normal bound on the same inputs."""
+    the tensor-core kernels stay inside the bf16 bound.  Around 3-4 times their accuracy degrades before their range
+    ends: for a few query rows the in-window low-rank estimate is a few huge, mutually cancelling terms, tens of
+    times the exact in-window mass, and features, KV and D = E - P rounded to bf16 leave errors relative to those
+    terms (9e-2 at 4x).  The kernels see this (the row sums of D and of E are at hand) and report it as "precision".
+    At 6x the exact part dominates again and the result is inside the bound.  The kernels never rescale an
+    accumulator, so their range is finite too: past it the call reports the numeric range (next test).  Here: a
+    call that reports nothing is inside the bf16 bound; the fp32-math kernels are inside it on all of these inputs."""
     from fly_b200 import ops, _cabi
     q, k, v, W = _inputs(1, 512, 512, 2, seed=17)
     q, k = (q.float() * factor).bfloat16(), (k.float() * factor).bfloat16()
@@ -226,13 +227,14 @@ def test_scaled_inputs(factor, bound, sbl_lib):
     assert so.rel_err(gen, ref) <= TOL_BF16
     pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), 256)
     out = pr.forward().float().cpu()
-    try:
-        pr.check_status()
-    except _cabi.SblError as exc:
-        assert 'numeric range' in str(exc)
+    if expect == 'precision':
+        with pytest.raises(_cabi.SblError, match='precision'):
+            pr.check_status()
+        assert torch.isfinite(out).all()
+        assert so.rel_err(out, ref) <= 0.2      # degraded, not garbage
         return
-    assert torch.isfinite(out).all()
-    assert so.rel_err(out, ref) <= bound
+    pr.check_status()
+    assert so.rel_err(out, ref) <= TOL_BF16
 
 
 def test_out_of_range_logits_are_reported(sbl_lib):
