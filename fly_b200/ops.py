@@ -173,10 +173,19 @@ class Problem:
         self._call(_cabi.load().sbl_key_logscale, beta.data_ptr(), workspace=workspace)
         return beta
 
-    def key_summary(self, beta, workspace=None):
+    def key_summary(self, beta, workspace=None, out=None):
+        """out: optional (kv, ksum) pair of contiguous fp32 tensors (B,H,m,D) and (B,H,m) to write into (a caller
+        that all-reduces both can make them two views of one buffer)."""
         B, H, _, _, _, D = self.shape
-        kv = torch.empty(B, H, self.m, D, device=self.device, dtype=torch.float32)
-        ksum = torch.empty(B, H, self.m, device=self.device, dtype=torch.float32)
+        if out is None:
+            kv = torch.empty(B, H, self.m, D, device=self.device, dtype=torch.float32)
+            ksum = torch.empty(B, H, self.m, device=self.device, dtype=torch.float32)
+        else:
+            kv, ksum = out
+            if (tuple(kv.shape) != (B, H, self.m, D) or tuple(ksum.shape) != (B, H, self.m)
+                    or kv.dtype != torch.float32 or ksum.dtype != torch.float32
+                    or not kv.is_contiguous() or not ksum.is_contiguous() or kv.device != self.device):
+                raise ValueError('out must be contiguous fp32 (B,H,m,D) and (B,H,m) tensors on the problem device')
         beta = beta.contiguous()
         self._call(_cabi.load().sbl_key_summary, beta.data_ptr(), kv.data_ptr(), ksum.data_ptr(),
                    workspace=workspace)

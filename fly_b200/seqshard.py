@@ -87,9 +87,13 @@ class HaloExchange:
             ops_ += [dist.P2POp(dist.isend, ks, _global_rank(peer, self.group), self.group),
                      dist.P2POp(dist.isend, vs, _global_rank(peer, self.group), self.group)]
         for peer, a, b in self.recvs:
-            kr = k_local.new_empty(B, b - a, H, E)
-            vr = v_local.new_empty(B, b - a, H, D)
-            self._landing.append((a, b, kr, vr))
+            # the rows land in place where the slice of the extended buffer is contiguous (B = 1), else in a
+            # buffer of their own that finish() copies from
+            kr, vr = self.k_ext[:, a - klo:b - klo], self.v_ext[:, a - klo:b - klo]
+            if not (kr.is_contiguous() and vr.is_contiguous()):
+                kr = k_local.new_empty(B, b - a, H, E)
+                vr = v_local.new_empty(B, b - a, H, D)
+                self._landing.append((a, b, kr, vr))
             ops_ += [dist.P2POp(dist.irecv, kr, _global_rank(peer, self.group), self.group),
                      dist.P2POp(dist.irecv, vr, _global_rank(peer, self.group), self.group)]
         if ops_:
@@ -129,8 +133,8 @@ class CudaEngine:
     def key_logscale(self):
         return self.prob.key_logscale(workspace=self.ws)
 
-    def key_summary(self, beta):
-        return self.prob.key_summary(beta, workspace=self.ws)
+    def key_summary(self, beta, out=None):
+        return self.prob.key_summary(beta, workspace=self.ws, out=out)
 
     def band_forward(self, beta, kv, ksum):
         return self.prob.band_forward(beta, kv, ksum, workspace=self.ws)
@@ -164,11 +168,13 @@ def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_tota
     halo.finish()
     beta_work.wait()
     mark('halo+max')
-    kv, ksum = eng.key_summary(beta)
+    # kv and ksum are two views of one buffer: one collective for both, no packing copies
+    B, H, D, m = q_local.shape[0], q_local.shape[2], v_local.shape[-1], 2 * W.shape[0]
+    packed = torch.empty(B * H * m * (D + 1), device=q_local.device, dtype=torch.float32)
+    views = (packed[:B * H * m * D].view(B, H, m, D), packed[B * H * m * D:].view(B, H, m))
+    kv, ksum = eng.key_summary(beta, out=views)
     mark('summary')
-    packed = torch.cat([kv, ksum.unsqueeze(-1)], dim=-1).contiguous()     # one collective for both
     dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
-    kv, ksum = packed[..., :-1].contiguous(), packed[..., -1].contiguous()
     mark('allreduce')
     out = eng.band_forward(beta, kv, ksum)
     mark('band')

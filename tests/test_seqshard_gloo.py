@@ -62,10 +62,15 @@ class OracleEngine:
         pos = self.klo + torch.arange(self.k.shape[2])
         return phik.masked_fill((pos.view(1, 1, -1, 1) >= self.lengths.view(-1, 1, 1, 1)), 0.0)
 
-    def key_summary(self, beta):
+    def key_summary(self, beta, out=None):
         a, b = self.lo - self.klo, self.lo - self.klo + self.n_own
         phik = self._phik(beta)[:, :, a:b]
-        return torch.einsum('bhsm,bhsd->bhmd', phik, self.v[:, :, a:b]), phik.sum(-2)
+        kv, ksum = torch.einsum('bhsm,bhsd->bhmd', phik, self.v[:, :, a:b]), phik.sum(-2)
+        if out is not None:
+            out[0].copy_(kv)
+            out[1].copy_(ksum)
+            return out
+        return kv, ksum
 
     def band_forward(self, beta, kv, ksum):
         so = self.so
