@@ -54,13 +54,37 @@ def plan_halo(bounds, w, rank):
     return sends, recvs
 
 
+class HaloBuffers:
+    """K/V storage of one rank that already has room for the halo rows on both sides.
+
+    A caller that writes its shard of K and V straight into `k_local` / `v_local` (views of the extended buffers)
+    and passes this object to `sblocal_forward_seqshard` saves the copy of the own rows into the extended buffers
+    that the forward otherwise makes on every call (two reads and two writes of the whole shard)."""
+
+    def __init__(self, B, n_total, H, E, D, local_context, dtype, device, group=None):
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        self.bounds = shard_bounds(n_total, world)
+        self.lo, self.hi = self.bounds[rank], self.bounds[rank + 1]
+        self.klo, self.khi = halo_range(self.lo, self.hi, int(local_context), n_total)
+        self.k_ext = torch.empty(B, self.khi - self.klo, H, E, dtype=dtype, device=device)
+        self.v_ext = torch.empty(B, self.khi - self.klo, H, D, dtype=dtype, device=device)
+        self.k_local = self.k_ext[:, self.lo - self.klo:self.hi - self.klo]
+        self.v_local = self.v_ext[:, self.lo - self.klo:self.hi - self.klo]
+
+    def holds(self, k_local, v_local):
+        return (k_local.data_ptr() == self.k_local.data_ptr() and v_local.data_ptr() == self.v_local.data_ptr()
+                and k_local.shape == self.k_local.shape and v_local.shape == self.v_local.shape
+                and k_local.stride() == self.k_local.stride() and v_local.stride() == self.v_local.stride())
+
+
 class HaloExchange:
     """Window-halo exchange in two steps, so that work which needs only the own rows can be queued in between.
 
     start(): allocates the extended K/V buffers, copies the own rows in and posts the point-to-point transfers
     (the landing buffers are this rank's own memory); finish(): waits for them and places the received rows."""
 
-    def __init__(self, k_local, v_local, bounds, w, group=None):
+    def __init__(self, k_local, v_local, bounds, w, group=None, buffers=None):
+        self.buffers = buffers
         self.rank = dist.get_rank(group)
         self.group = group
         self.lo, self.hi = bounds[self.rank], bounds[self.rank + 1]
@@ -75,10 +99,14 @@ class HaloExchange:
         k_local, v_local, lo, hi, klo, khi = self.k_local, self.v_local, self.lo, self.hi, self.klo, self.khi
         B, _, H, E = k_local.shape
         D = v_local.shape[-1]
-        self.k_ext = k_local.new_empty(B, khi - klo, H, E)
-        self.v_ext = v_local.new_empty(B, khi - klo, H, D)
-        self.k_ext[:, lo - klo:hi - klo] = k_local
-        self.v_ext[:, lo - klo:hi - klo] = v_local
+        if self.buffers is not None:
+            # the own rows already sit in the middle of the caller's extended buffers
+            self.k_ext, self.v_ext = self.buffers.k_ext, self.buffers.v_ext
+        else:
+            self.k_ext = k_local.new_empty(B, khi - klo, H, E)
+            self.v_ext = v_local.new_empty(B, khi - klo, H, D)
+            self.k_ext[:, lo - klo:hi - klo] = k_local
+            self.v_ext[:, lo - klo:hi - klo] = v_local
         ops_ = []
         for peer, a, b in self.sends:
             ks = k_local[:, a - lo:b - lo].contiguous()
@@ -141,7 +169,8 @@ class CudaEngine:
 
 
 def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_total, softmax_temp=None,
-                             softmax_eps=0.0, key_lengths=None, group=None, engine_cls=CudaEngine, timings=None):
+                             softmax_eps=0.0, key_lengths=None, group=None, engine_cls=CudaEngine, timings=None,
+                             halo_buffers=None):
     """SBLocal forward of this rank's shard of one long sequence.
 
     q_local/k_local/v_local: (B, n_local, H, E|D), rows
@@ -149,6 +178,8 @@ def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_tota
     key_lengths: global (B,) key lengths or None.  Returns out (B, n_local, H, D).
     timings: an empty list to be filled with (stage name, CUDA event) pairs recorded on the current stream
     after each stage (CUDA ranks only).
+    halo_buffers: a `HaloBuffers` whose k_local / v_local views ARE k_local / v_local: the own rows are then used
+    where they are instead of being copied next to the halo rows.
     """
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     bounds = shard_bounds(n_total, world)
@@ -159,7 +190,9 @@ def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_tota
     # all-reduce travels with them.  The summary and the band stage need the halo rows / the reduced summary.
     mark = (lambda name: None) if timings is None else (lambda name: timings.append((name, _event())))
     mark('start')
-    halo = HaloExchange(k_local, v_local, bounds, int(local_context), group).start()
+    if halo_buffers is not None and not (halo_buffers.bounds == bounds and halo_buffers.holds(k_local, v_local)):
+        raise ValueError('halo_buffers must be the HaloBuffers object whose k_local / v_local views are passed in')
+    halo = HaloExchange(k_local, v_local, bounds, int(local_context), group, halo_buffers).start()
     eng = engine_cls(q_local, halo.k_ext, halo.v_ext, W, int(local_context), softmax_temp, softmax_eps, key_lengths,
                      lo, halo.klo, n_total, hi - lo)
     beta = eng.key_logscale()

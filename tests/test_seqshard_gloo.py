@@ -118,6 +118,15 @@ def _worker(rank, world, port, case, ret):
                                        engine_cls=OracleEngine)
         ref, _ = so.sblocal_forward(q, k, v, W, w, None, eps, lengths)
         ret[rank] = so.rel_err(out, ref[:, lo:hi]) if hi > lo else 0.0
+        # the same with the own rows written straight into caller-owned extended buffers (no copy of the shard)
+        from fly_b200.seqshard import HaloBuffers
+        hb = HaloBuffers(B, N, H, E, D, w, q.dtype, q.device)
+        hb.k_local.copy_(k[:, lo:hi])
+        hb.v_local.copy_(v[:, lo:hi])
+        out2 = sblocal_forward_seqshard(q[:, lo:hi], hb.k_local, hb.v_local, W, w, N, None, eps, lengths,
+                                        engine_cls=OracleEngine, halo_buffers=hb)
+        if hi > lo:
+            ret[rank] = max(ret[rank], so.rel_err(out2, ref[:, lo:hi]))
     finally:
         dist.destroy_process_group()
 

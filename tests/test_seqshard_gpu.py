@@ -36,6 +36,14 @@ def _worker(rank, world, port, dtype_name, ret):
         torch.cuda.synchronize()
         ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
         ret[rank] = so.rel_err(out.float().cpu(), ref[:, lo:hi])
+        # the same with the shard's K/V written in place into caller-owned halo-extended buffers
+        from fly_b200.seqshard import HaloBuffers
+        hb = HaloBuffers(B, N, H, E, E, w, dtype, dev)
+        hb.k_local.copy_(k[:, lo:hi])
+        hb.v_local.copy_(v[:, lo:hi])
+        out2 = sblocal_forward_seqshard(q[:, lo:hi].to(dev), hb.k_local, hb.v_local, W.to(dev), w, N, halo_buffers=hb)
+        torch.cuda.synchronize()
+        ret[rank] = max(ret[rank], so.rel_err(out2.float().cpu(), ref[:, lo:hi]))
     finally:
         dist.destroy_process_group()
 
