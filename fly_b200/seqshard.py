@@ -9,10 +9,9 @@ cf. src/models/attention/sblocal_attention.py:87-97 and
 src/models/attention/feature_maps_sb.py:78.
 
 Protocol per forward (rank g owns rows [lo, hi) of q, k, v, out):
-  1. halo exchange: every rank sends the K/V rows other ranks' windows reach
-     into (point-to-point, into the receivers' own memory); posted first and
-     waited for only after step 2 has been queued, which needs no halo row;
-  2. sbl_key_logscale over the own rows        -> all-reduce MAX of (B,H) floats;
+  1. sbl_key_logscale over the own rows (queued first: the device runs it while the host posts step 2);
+  2. halo exchange: every rank sends the K/V rows other ranks' windows reach into (point-to-point, into the
+     receivers' own memory), with the all-reduce MAX of the (B,H) log-scales travelling beside it;
   3. sbl_key_summary over own rows (+phi(K) of the halo rows kept in the
      workspace)                                -> all-reduce SUM of (B,H,m,D+1) floats;
   4. sbl_band_forward over the local queries, reading local memory only.
@@ -80,8 +79,9 @@ class HaloBuffers:
 class HaloExchange:
     """Window-halo exchange in two steps, so that work which needs only the own rows can be queued in between.
 
-    start(): allocates the extended K/V buffers, copies the own rows in and posts the point-to-point transfers
-    (the landing buffers are this rank's own memory); finish(): waits for them and places the received rows."""
+    prepare(): the extended K/V buffers with the own rows in place (the caller's `HaloBuffers`, or fresh ones the
+    own rows are copied into); start(): posts the point-to-point transfers (the landing buffers are this rank's own
+    memory); finish(): waits for them and places the received rows."""
 
     def __init__(self, k_local, v_local, bounds, w, group=None, buffers=None):
         self.buffers = buffers
@@ -95,7 +95,7 @@ class HaloExchange:
         self.k_ext = self.v_ext = None
         self._reqs, self._landing, self._keep = [], [], []
 
-    def start(self):
+    def prepare(self):
         k_local, v_local, lo, hi, klo, khi = self.k_local, self.v_local, self.lo, self.hi, self.klo, self.khi
         B, _, H, E = k_local.shape
         D = v_local.shape[-1]
@@ -107,6 +107,14 @@ class HaloExchange:
             self.v_ext = v_local.new_empty(B, khi - klo, H, D)
             self.k_ext[:, lo - klo:hi - klo] = k_local
             self.v_ext[:, lo - klo:hi - klo] = v_local
+        return self
+
+    def start(self):
+        if self.k_ext is None:
+            self.prepare()
+        k_local, v_local, lo, klo = self.k_local, self.v_local, self.lo, self.klo
+        B, _, H, E = k_local.shape
+        D = v_local.shape[-1]
         ops_ = []
         for peer, a, b in self.sends:
             ks = k_local[:, a - lo:b - lo].contiguous()
@@ -186,17 +194,19 @@ def sblocal_forward_seqshard(q_local, k_local, v_local, W, local_context, n_tota
     lo, hi = bounds[rank], bounds[rank + 1]
     if q_local.shape[1] != hi - lo or k_local.shape[1] != hi - lo or v_local.shape[1] != hi - lo:
         raise ValueError(f'rank {rank} must hold rows [{lo},{hi}) of the sequence: got {q_local.shape[1]} rows')
-    # The key log-scale reads the own rows only: it is queued while the halo rows are in flight, and its MAX
-    # all-reduce travels with them.  The summary and the band stage need the halo rows / the reduced summary.
+    # The key log-scale reads the own rows only: the halo rows fly while it runs, and its MAX all-reduce travels
+    # with them.  The summary and the band stage need the halo rows / the reduced summary.
     mark = (lambda name: None) if timings is None else (lambda name: timings.append((name, _event())))
     mark('start')
     if halo_buffers is not None and not (halo_buffers.bounds == bounds and halo_buffers.holds(k_local, v_local)):
         raise ValueError('halo_buffers must be the HaloBuffers object whose k_local / v_local views are passed in')
-    halo = HaloExchange(k_local, v_local, bounds, int(local_context), group, halo_buffers).start()
+    # The log-scale pass is queued first: the device works on it while the host sets up the transfers.
+    halo = HaloExchange(k_local, v_local, bounds, int(local_context), group, halo_buffers).prepare()
     eng = engine_cls(q_local, halo.k_ext, halo.v_ext, W, int(local_context), softmax_temp, softmax_eps, key_lengths,
                      lo, halo.klo, n_total, hi - lo)
     beta = eng.key_logscale()
     mark('logscale')
+    halo.start()
     beta_work = dist.all_reduce(beta, op=dist.ReduceOp.MAX, group=group, async_op=True)
     halo.finish()
     beta_work.wait()
