@@ -489,6 +489,8 @@ def main():
     if world > 1:
         # the collectives of the side measurements are small and latency-bound; keep them on plain rings
         os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+        # NCCL writes its version / debug lines to stdout by default; stdout carries the one JSON line
+        os.environ.setdefault('NCCL_DEBUG_FILE', '/dev/stderr')
         dist.init_process_group('nccl', device_id=dev)
     args.warmup = max(args.warmup, 3)
     spec = WORKLOADS[args.workload]
