@@ -209,7 +209,7 @@ def run_reference(args, spec, rank):
                 cpu_baseline=dict(value=value, unit='tokens/s', cores=cores, kind=kind,
                                   sample=cpu_sample_text(units, spec, kind)),
                 e2e=dict(value=value, unit='tokens/s', h2d_bytes_per_step=0, d2h_bytes_per_step=0))
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def timed_blocks(run_step, steps, reps, barrier, flush=None):
@@ -446,7 +446,18 @@ def run_t2t(args, dev):
                 e2e=dict(value=out['fp32_attention']['images_per_s'], unit='images/s',
                          h2d_bytes_per_step=img_h.numel() * 4, d2h_bytes_per_step=logits_h.numel() * 4),
                 variants=out)
-    print(json.dumps(line))
+    emit(json.dumps(line))
+
+
+_RESULT_FD = None
+
+
+def emit(text):
+    """Writes the result line to the process's original stdout."""
+    if _RESULT_FD is None:
+        print(text, flush=True)
+    else:
+        os.write(_RESULT_FD, (text + '\n').encode())
 
 
 def main():
@@ -465,6 +476,12 @@ def main():
     ap.add_argument('--profile', action='store_true',
                     help='run only warm-up and the timed forwards (for ncu captures); prints no JSON line')
     args = ap.parse_args()
+    # stdout carries the one result line: whatever libraries write to file descriptor 1 on the way (NCCL prints
+    # its version there) is sent to stderr instead
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get('RANK', '0'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -489,8 +506,6 @@ def main():
     if world > 1:
         # the collectives of the side measurements are small and latency-bound; keep them on plain rings
         os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
-        # NCCL writes its version / debug lines to stdout by default; stdout carries the one JSON line
-        os.environ.setdefault('NCCL_DEBUG_FILE', '/dev/stderr')
         dist.init_process_group('nccl', device_id=dev)
     args.warmup = max(args.warmup, 3)
     spec = WORKLOADS[args.workload]
@@ -536,7 +551,7 @@ def main():
         clocks['sampled_over'] = 'timed blocks + 0.6 s untimed repeat of the same step, nvidia-smi every 50 ms'
     if args.profile:
         prob.check_status()
-        print(f'profile run: {block_ms[0] / args.steps:.4f} ms per forward (not a benchmark value)')
+        emit(f'profile run: {block_ms[0] / args.steps:.4f} ms per forward (not a benchmark value)')
         return
 
     # ---- per-stage timing on the launch stream (roofline of the band kernel) ----
@@ -709,7 +724,7 @@ def main():
             dq, dk, dv = (x.to(dev).to(q.dtype) for x in (cq, ck, cv))
             got = ops.sblocal_forward(dq, dk, dv, cW.to(dev), w).float().cpu()
             line['parity_vs_cpu_sample'] = so.rel_err(got, ref_out)
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
