@@ -438,34 +438,37 @@ constexpr int W_LOAD = 16;                 // producer warp
 constexpr int W_MMA = 17;                  // MMA issuer warp
 constexpr int NTHREADS = NSOFT + 64;
 constexpr uint32_t OFF_Q = 0;              // 32 KB: two blocks [128 q][64 e]
-constexpr uint32_t OFF_RING = 32768;       // ring of 32 KB slots: every B operand, and the staged output tile
-// Six slots: with five, the refill of a slot (MMAs done -> load issued -> data landed) took a little longer than
-// the issuer needs for the five pieces in between, and every piece was waited for.  Six slots and the Q tile
-// leave 2.5 KB of the 227 KB: the feature sums are read from global memory (L1), the row sums of D are exchanged
-// through the output staging slot, and the kernel relies on (and checks) a 1024-byte aligned shared-memory base.
-constexpr uint32_t NSLOT = 6, SLOT = 32768;
+constexpr uint32_t OFF_PHI1 = 32768;       // 64 KB: feature half 1 of phi(Q), bf16, four blocks [128 q][64 f] (A operand)
+constexpr uint32_t OFF_RING = OFF_PHI1 + 65536;   // ring of 32 KB slots: every B operand, and the staged output tile
+// Four slots, the Q tile and half of phi(Q) leave 2.5 KB of the 227 KB: the feature sums are read from global memory
+// (L1), the row sums of D are exchanged through the output staging slot, and the kernel relies on (and checks) a
+// 1024-byte aligned shared-memory base.  (The ring is not deeper for a reason: what limits the operand stream is
+// the rate at which one SM takes data in, 32 KB per 785 cycles whatever the depth.)
+constexpr uint32_t NSLOT = 4, SLOT = 32768;
 constexpr uint32_t OFF_MISC = OFF_RING + NSLOT * SLOT;   // (L, Z) fp32[2][2][128]
 constexpr uint32_t OFF_BAR = OFF_MISC + 2048;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512;
 static_assert(SMEM_BYTES <= 232448, "dynamic shared memory of one CTA");
 // tensor memory columns (512)
 constexpr uint32_t T_O = 0;        // 128
-constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, then E, then E - P (fp32), then D packed bf16 in place
-constexpr uint32_t T_PHI = 384;    // 128: U half (fp32), then 256 bf16 features in place
+constexpr uint32_t T_BUF = 128;    // 2 x 128: S of a key tile, then E, then E - P (fp32), then D packed bf16 in place;
+                                   //          at the start of a query tile one of them holds U half 1
+constexpr uint32_t T_PHI = 384;    // 128: U half 0 (fp32), then 256 bf16 features in place
 enum {
   B_QFULL = 0,                    // Q tile landed
   B_QFREE,                        // Q buffer reusable: last MMA reading it + one arrival per exponential warp
   B_FULL,                         // [NSLOT] ring slot landed
   B_EMPTY = B_FULL + NSLOT,       // [NSLOT] ring slot consumed (MMAs done, or the output store has read it)
-  B_UFULL = B_EMPTY + NSLOT,      // U half computed
-  B_PHIFULL,                      // features formed in place (one arrival per exponential warp)
-  B_SFULL,                        // [2] S computed into the buffer
+  B_UFULL = B_EMPTY + NSLOT,      // [2] U half computed
+  B_PHIFULL = B_UFULL + 2,        // [2] features of the half formed (one arrival per exponential warp)
+  B_SFULL = B_PHIFULL + 2,        // [2] S computed into the buffer
   B_EDONE = B_SFULL + 2,          // [2] E written (one arrival per exponential warp)
   B_PDONE = B_EDONE + 2,          // [2] P subtracted
   B_DDONE = B_PDONE + 2,          // [2] D packed (one arrival per packing warp)
   B_OFREE = B_DDONE + 2,          // O read by the epilogue (one arrival per packing warp)
   B_DONE,                         // all MMAs of the query tile done
   B_LZFULL,                       // L and Z of the query tile published by the exponential group
+  B_LZFREE,                       // ... and read by the packing group (one arrival per packing warp)
   B_OUTREADY,                     // the ring slot that stages this tile's output is free
   B_COUNT
 };
@@ -515,13 +518,12 @@ struct RingPos {
   }
 };
 
-// Per query tile with nt key tiles, the ring carries 7 + 7 nt pieces in this order (the order of the issuer's
+// Per query tile with nt key tiles, the ring carries 7 + 6 nt pieces in this order (the order of the issuer's
 // MMA groups):
-//   Wt half 0 | K(0), K(1) | KV half 0 (2) |
-//   pass A, t = 0..nt:  phi(K)_0(t) (2) [t < nt] | Wt half 1 [t = nt] | V(t-1) [t >= 1] | K(t+1) [1 <= t, t+1 < nt] |
-//   KV half 1 (2) |
-//   pass B, t = 0..nt:  phi(K)_1(t) (2) [t < nt] | V(t-1) [t >= 1] |
+//   Wt half 0 | Wt half 1 | K(0) | KV half 0 (2) | K(1) | KV half 1 (2) |
+//   t = 0..nt:  phi(K)_0(t) (2), phi(K)_1(t) (2) [t < nt] | V(t-1) [t >= 1] | K(t+1) [1 <= t, t+1 < nt] |
 //   the output staging slot
+// Key tile t of a query tile uses buffer (G + t) & 1, G = key tiles of the earlier query tiles of this CTA.
 __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const __grid_constant__ Band128Args a) {
   using namespace band128;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -541,8 +543,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
   if (warp == W_MMA) {
     for (int i = lane; i < B_COUNT; i += 32) {
       int count = 1;
-      if (i == B_PHIFULL || (i >= B_EDONE && i < B_EDONE + 2) || (i >= B_DDONE && i < B_DDONE + 2) || i == B_OFREE ||
-          i == B_LZFULL)
+      if ((i >= B_PHIFULL && i < B_PHIFULL + 2) || (i >= B_EDONE && i < B_EDONE + 2) ||
+          (i >= B_DDONE && i < B_DDONE + 2) || i == B_OFREE || i == B_LZFULL || i == B_LZFREE)
         count = WGRP;
       if (i == B_QFREE) count = WGRP + 1;
       mbar_init(bars + i, count);
@@ -634,8 +636,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       if (have_next) Tn = tile128(a, it + 1);
       const int nt = T.nt;
       // Pull the diagonal key tile of the NEXT query tile (K, V, phi(K): 192 KB) into L2 now.  The CTAs of the grid
-      // work on neighbouring query tiles, so between them they prefetch every key tile the grid's next round
-      // reads, and the ring loads of that round find their data in L2 instead of waiting for HBM.
+      // work on neighbouring query tiles, so between them they prefetch every key tile the grid's next round reads.
       if (have_next && leader) {
         const int row0 = (int)(p.q_pos0 + Tn.i0 - p.k_pos0) / KT * KT;
         if (row0 >= Tn.j0 && row0 < Tn.j0 + Tn.nt * KT) {
@@ -649,23 +650,27 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         }
       }
       load_w(0);
-      for (int t = 0; t < min(nt, 2); ++t) load_rows(&a.tm_k, T, t);
+      load_w(1);
+      if (nt > 0) load_rows(&a.tm_k, T, 0);
       load_kv(T, 0);
+      if (nt > 1) load_rows(&a.tm_k, T, 1);
+      load_kv(T, 1);
+      bool q_loaded = false;
 #pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-#pragma unroll 1
-        for (int t = 0; t <= nt; ++t) {
-          if (t < nt) load_phik(T, pass, t);
-          if (pass == 0 && t == nt) load_w(1);
-          if (pass == 1 && t == 0 && have_next) {
-            // the Q buffer is free once the second U half has run (five pieces back in the ring by now)
-            ph.wait(bars, B_QFREE, a.status, 151);
-            load_q(Tn);
-          }
-          if (t >= 1) load_rows(&a.tm_v, T, t - 1);
-          if (pass == 0 && t >= 1 && t + 1 < nt) load_rows(&a.tm_k, T, t + 1);
+      for (int t = 0; t <= nt; ++t) {
+        if (t < nt) {
+          load_phik(T, 0, t);
+          load_phik(T, 1, t);
         }
-        if (pass == 0) load_kv(T, 1);
+        if (have_next && !q_loaded && t >= nt - 1) {
+          // every S of this tile and both U halves have been issued by now (their pieces are at least four
+          // back in the ring): the Q buffer is about to be free
+          ph.wait(bars, B_QFREE, a.status, 151);
+          load_q(Tn);
+          q_loaded = true;
+        }
+        if (t >= 1) load_rows(&a.tm_v, T, t - 1);
+        if (t >= 1 && t + 1 < nt) load_rows(&a.tm_k, T, t + 1);
       }
       // the slot that stages the output tile: hand it to the packing group
       acquire();
@@ -680,6 +685,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
     constexpr uint32_t id_mn = idesc_bf16(128, 128, false, true);              // low-rank, O: B = [K index][128 d]
     constexpr uint32_t id_neg = idesc_bf16(128, 128, false, false) | (1u << 13);   // P: bit 13 negates A
     const uint64_t dQ = smem_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
+    const uint64_t dPhi1 = smem_desc_sw128(smem_u32(smem + OFF_PHI1), 16, 1024);
     const uint64_t dRingK = smem_desc_sw128(smem_u32(smem + OFF_RING), 16, 1024);       // K-major piece
     const uint64_t dRingMN = smem_desc_sw128(smem_u32(smem + OFF_RING), 16384, 1024);   // MN-major piece
     Phases ph;
@@ -690,7 +696,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       rp.advance();
       return s;
     };
-    // K step k of a K-major operand of two 64-column blocks
+    // K step k of a K-major operand made of 64-column blocks 16 KB apart
     auto koff = [](int k) { return (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2); };
     auto issue_qk = [&](uint32_t td, uint64_t* full_bar) {   // td = Q x (piece)^T: S or a U half
       const uint32_t s = take();
@@ -704,34 +710,41 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       }
       __syncwarp();
     };
-    auto issue_lr = [&](int half) {   // O (+)= phi(Q)_half KV_half
-      ph.wait(bars, B_PHIFULL, a.status, 161);
+    auto issue_lr = [&](int half) {   // O (+)= phi(Q)_half KV_half: half 0 from tensor memory, half 1 from shared memory
+      ph.wait(bars, B_PHIFULL + half, a.status, 161);
       for (int fg = 0; fg < 2; ++fg) {
         const uint32_t s = take();
         tc_fence_after_sync();
         if (leader) {
           const uint64_t dB = dRingMN + (uint64_t)(s * (SLOT >> 4));
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            mma_ts(tb + T_O, tb + T_PHI + 8 * (8 * fg + k), dB + (uint64_t)(k * (2048 >> 4)), id_mn,
-                   half != 0 || fg != 0 || k != 0);
+          for (int k = 0; k < 8; ++k) {
+            if (half == 0)
+              mma_ts(tb + T_O, tb + T_PHI + 8 * (8 * fg + k), dB + (uint64_t)(k * (2048 >> 4)), id_mn, fg != 0 || k != 0);
+            else
+              mma_ss(tb + T_O, dPhi1 + koff(8 * fg + k), dB + (uint64_t)(k * (2048 >> 4)), id_mn, true);
+          }
           mma_commit(bars + B_EMPTY + s);
         }
         __syncwarp();
       }
     };
-    auto issue_p = [&](int half, int buf) {   // buffer (-)= phi(Q)_half phi(K)_half^T
-      for (int j = 0; j < 2; ++j) {
+    auto issue_p = [&](int buf) {   // buffer -= phi(Q) phi(K)^T: half 0 (A in tensor memory), then half 1 (A in shared memory)
+      ph.wait(bars, B_EDONE + buf, a.status, 165);
+      for (int j = 0; j < 4; ++j) {
         const uint32_t s = take();
         tc_fence_after_sync();
         if (leader) {
           const uint64_t dB = dRingK + (uint64_t)(s * (SLOT >> 4));
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            mma_ts(tb + T_BUF + buf * 128, tb + T_PHI + 8 * (8 * j + k), dB + koff(k), id_neg,
-                   half == 0 || j != 0 || k != 0);
+          for (int k = 0; k < 8; ++k) {
+            if (j < 2)
+              mma_ts(tb + T_BUF + buf * 128, tb + T_PHI + 8 * (8 * j + k), dB + koff(k), id_neg, true);
+            else
+              mma_ss(tb + T_BUF + buf * 128, dPhi1 + koff(8 * (j - 2) + k), dB + koff(k), id_neg, true);
+          }
           mma_commit(bars + B_EMPTY + s);
-          if (j == 1) mma_commit(bars + B_PDONE + buf);
+          if (j == 3) mma_commit(bars + B_PDONE + buf);
         }
         __syncwarp();
       }
@@ -750,42 +763,50 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       }
       __syncwarp();
     };
+    int G = 0;
 #pragma unroll 1
     for (int it = 0; it < n_it; ++it) {
       const int nt = tile128(a, it).nt;
+      const int b0 = G & 1, b1 = b0 ^ 1;       // buffers of this tile's key tiles 0 and 1
       ph.wait(bars, B_QFULL, a.status, 163);
-      issue_qk(tb + T_PHI, bars + B_UFULL);
-      for (int t = 0; t < min(nt, 2); ++t) issue_qk(tb + T_BUF + t * 128, bars + B_SFULL + t);
-      if (it >= 1) ph.wait(bars, B_OFREE, a.status, 164);   // the previous tile's epilogue has read O
+      issue_qk(tb + T_PHI, bars + B_UFULL);                     // U half 0: features formed in place
+      issue_qk(tb + T_BUF + b1 * 128, bars + B_UFULL + 1);      // U half 1: parked in the buffer of key tile 1
+      if (nt > 0) issue_qk(tb + T_BUF + b0 * 128, bars + B_SFULL + b0);
+      if (it >= 1) ph.wait(bars, B_OFREE, a.status, 164);       // the previous tile's epilogue has read O
       issue_lr(0);
+      // feature half 1 has been written to shared memory: its U is out of the buffer
+      if (nt > 1) {
+        ph.wait(bars, B_PHIFULL + 1, a.status, 166);
+        ph.bits ^= 1u << (B_PHIFULL + 1);                       // issue_lr(1) waits for the same phase again
+        issue_qk(tb + T_BUF + b1 * 128, bars + B_SFULL + b1);
+      }
+      issue_lr(1);
+      if (nt <= 2) {                                            // no later MMA of this tile reads Q
+        if (leader) mma_commit(bars + B_QFREE);
+        __syncwarp();
+      }
 #pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-        // a tile has 2 nt steps, so the buffer of pass A step t is t & 1, of pass B step t (nt + t) & 1
-#pragma unroll 1
-        for (int t = 0; t <= nt; ++t) {
-          const int buf = (pass * nt + t) & 1;
-          if (t < nt) {
-            if (pass == 0) ph.wait(bars, B_EDONE + buf, a.status, 165);
-            issue_p(pass, buf);
-          }
-          if (pass == 0 && t == nt) {
-            issue_qk(tb + T_PHI, bars + B_UFULL);            // second U half: every P_0 has been issued
-            if (leader) mma_commit(bars + B_QFREE);           // no later MMA of this tile reads Q
+      for (int t = 0; t <= nt; ++t) {
+        const int buf = (G + t) & 1;
+        if (t < nt) issue_p(buf);
+        if (t >= 1) issue_o(buf ^ 1);
+        if (t >= 1 && t + 1 < nt) {
+          issue_qk(tb + T_BUF + (buf ^ 1) * 128, bars + B_SFULL + (buf ^ 1));
+          if (t + 2 == nt) {                                    // that was the last S
+            if (leader) mma_commit(bars + B_QFREE);
             __syncwarp();
           }
-          if (t >= 1) issue_o(buf ^ 1);
-          if (pass == 0 && t >= 1 && t + 1 < nt) issue_qk(tb + T_BUF + (buf ^ 1) * 128, bars + B_SFULL + (buf ^ 1));
         }
-        if (pass == 0) issue_lr(1);
       }
       if (leader) mma_commit(bars + B_DONE);
       __syncwarp();
       rp.advance();   // the output staging slot
+      G += nt;
     }
   } else {
     // ---------------- softmax warps ----------------
     // Exponential group (warps 0-7): the features of both halves, E = exp(tau S - pls) of every key tile, the row
-    //   sums L and Z.  Packing group (warps 8-15): D -> bf16 for every step of both passes, its row sum, the epilogue.
+    //   sums L and Z.  Packing group (warps 8-15): D -> bf16 for every key tile, its row sum, the epilogue.
     // A thread of either group owns one query row and 64 columns (two chunks of 32) of every buffer.
     const int qd = warp & 3, cq = (warp >> 2) & 1;   // lane quarter (rows), column half
     const bool exp_group = warp < WGRP;
@@ -808,16 +829,20 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       return G;
     };
     Phases ph;
+    int G = 0;
     if (exp_group) {
       const float wmax = __ldg(a.wmax);
       const float half_log_m = 0.5f * logf((float)kM);
       const float sc = p.softmax_temp * kLog2e;
       const float* ksum_bh = a.ksum;   // feature sums of the current (b,h), internal order
       float M = 0.f;
-      // Features of one half, in place: this thread's 64 projections (four groups of 16 fp32 columns) become, per
-      // group, 16 "+" and 16 "-" features (2 x 8 packed columns); returns its share of phi(Q) . sum phi(K).
-      auto form_half = [&](int half) {
-        ph.wait(bars, B_UFULL, a.status, 170);
+      // Features of one half: this thread's 64 projections (four groups of 16 fp32 columns) become, per group,
+      // 16 "+" and 16 "-" features; returns its share of phi(Q) . sum phi(K).  Half 0 is written back in place
+      // (2 x 8 packed columns per group: the A operand in tensor memory), half 1 is read from the buffer its U was
+      // parked in and written to shared memory as a K-major bf16 operand (64 bytes of the row's 128-byte line of
+      // block c / 2, 16-byte chunks XORed with row % 8).
+      auto form_half = [&](int half, uint32_t tsrc) {
+        ph.wait(bars, B_UFULL + half, a.status, 170);
         tc_fence_after_sync();
         const float mo = -M * kLog2e;
         const float2 mo2 = make_float2(mo, mo);
@@ -826,7 +851,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
 #pragma unroll 1
         for (int g2 = 0; g2 < 4; ++g2) {
           const int c = 4 * cq + g2;               // group of 16 projections inside the half
-          const uint32_t taddr = lane_base + T_PHI + 16 * c;
+          const uint32_t taddr = lane_base + tsrc + 16 * c;
           const float* ks = ksum_bh + 256 * half + 32 * c;
           uint32_t r[16];
           tmem_ld16(taddr, r);
@@ -843,12 +868,21 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
             zz = fma2(ep, __ldg(reinterpret_cast<const float2*>(ks + 2 * j)), zz);
             zz = fma2(em, __ldg(reinterpret_cast<const float2*>(ks + 16 + 2 * j)), zz);
           }
-          tmem_st8(taddr, p1);
-          tmem_st8(taddr + 8, p2);
+          if (half == 0) {
+            tmem_st8(taddr, p1);
+            tmem_st8(taddr + 8, p2);
+          } else {
+            uint8_t* line = smem + OFF_PHI1 + (c >> 1) * 16384 + row * 128;
+            const int q0 = 4 * (c & 1);
+            *reinterpret_cast<uint4*>(line + (((q0 + 0) ^ (row & 7)) << 4)) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+            *reinterpret_cast<uint4*>(line + (((q0 + 1) ^ (row & 7)) << 4)) = make_uint4(p1[4], p1[5], p1[6], p1[7]);
+            *reinterpret_cast<uint4*>(line + (((q0 + 2) ^ (row & 7)) << 4)) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
+            *reinterpret_cast<uint4*>(line + (((q0 + 3) ^ (row & 7)) << 4)) = make_uint4(p2[4], p2[5], p2[6], p2[7]);
+          }
         }
-        tmem_st_wait();
+        if (half == 0) tmem_st_wait(); else fence_async_smem();
         tc_fence_before_sync();
-        warp_arrive(bars + B_PHIFULL, lane);
+        warp_arrive(bars + B_PHIFULL + half, lane);
         return zz.x + zz.y;
       };
 #pragma unroll 1
@@ -863,7 +897,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         const float gq = 0.5f * p.softmax_temp * qn2;
         M = sqrtf(qn2) * wmax;
         const float beta = __ldg(a.beta + T.bh);
-        float z = form_half(0);
+        float z = form_half(0, T_PHI);
+        z += form_half(1, T_BUF + ((G + 1) & 1) * 128);
         const int gi = (int)p.q_pos0 + T.i0 + row;     // global query position
         const float pls = (-gq + M - half_log_m) + beta;               // query log-scale + key log-scale
         const float2 sc2 = make_float2(sc, sc);
@@ -872,13 +907,13 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
 #pragma unroll 1
         for (int t = 0; t < nt; ++t) {
           // S(t) -> E = exp(tau S - pls) in place (fp32), zero outside the window; row sum
-          const int s = t & 1;
+          const int s = (G + t) & 1;
           ph.wait(bars, B_SFULL + s, a.status, 172);
           tc_fence_after_sync();
 #pragma unroll 1
           for (int ch = 0; ch < 2; ++ch) {
-            const Geo G = geometry(gi, (int)p.k_pos0 + T.j0 + t * KT + c0 + 32 * ch, T.len_b);
-            if (G.none) continue;   // a chunk nobody sees is left as it is: the packing group writes zeros for it
+            const Geo Gm = geometry(gi, (int)p.k_pos0 + T.j0 + t * KT + c0 + 32 * ch, T.len_b);
+            if (Gm.none) continue;   // a chunk nobody sees is left as it is: the packing group writes zeros for it
             const uint32_t tcol = lane_base + T_BUF + s * 128 + c0 + 32 * ch;
             uint32_t rs[32];
             tmem_ld32(tcol, rs);
@@ -888,8 +923,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
             for (int j = 0; j < 16; ++j) {
               const float2 x = fma2(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2, co2);
               float2 e = make_float2(0.f, 0.f);
-              if (G.vis & (1u << (2 * j))) e.x = ex2(x.x);          // predicated: hidden columns cost no exponential
-              if (G.vis & (2u << (2 * j))) e.y = ex2(x.y);
+              if (Gm.vis & (1u << (2 * j))) e.x = ex2(x.x);          // predicated: hidden columns cost no exponential
+              if (Gm.vis & (2u << (2 * j))) e.y = ex2(x.y);
               l2 = add2(l2, e);
               rs[2 * j] = __float_as_uint(e.x);
               rs[2 * j + 1] = __float_as_uint(e.y);
@@ -901,9 +936,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           tc_fence_before_sync();
           warp_arrive(bars + B_EDONE + s, lane);
         }
-        z += form_half(1);
-        // The packing group has read the previous tile's L and Z: it does so before it releases O, and this
-        // tile's second U half is issued behind the low-rank product that waits for that release.
+        G += nt;
+        // the packing group has read the previous tile's L and Z
+        if (it >= 1) ph.wait(bars, B_LZFREE, a.status, 173);
         s_lz[cq * 128 + row] = L;
         s_lz[256 + cq * 128 + row] = z;
         warp_arrive(bars + B_LZFULL, lane);
@@ -915,21 +950,21 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         const Tile128 T = tile128(a, it);
         const int nt = T.nt;
         const int gi = (int)p.q_pos0 + T.i0 + row;
-        float sd = 0.f;            // row sum of D over this thread's columns, both passes
+        float sd = 0.f;            // row sum of D over this thread's columns
 #pragma unroll 1
-        for (int step = 0; step < 2 * nt; ++step) {
-          // (E - P_0) or (-P_1), fp32, left by the tensor core -> masked, packed bf16 over the first 16 of every 32
-          // columns of this thread
-          const int t = step < nt ? step : step - nt, s = step & 1;
+        for (int t = 0; t < nt; ++t) {
+          // E - P, fp32, left by the tensor core -> masked, packed bf16 over the first 16 of every 32 columns of
+          // this thread
+          const int s = (G + t) & 1;
           ph.wait(bars, B_PDONE + s, a.status, 180);
           tc_fence_after_sync();
 #pragma unroll 1
           for (int ch = 0; ch < 2; ++ch) {
-            const Geo G = geometry(gi, (int)p.k_pos0 + T.j0 + t * KT + c0 + 32 * ch, T.len_b);
+            const Geo Gm = geometry(gi, (int)p.k_pos0 + T.j0 + t * KT + c0 + 32 * ch, T.len_b);
             const uint32_t tcol = lane_base + T_BUF + s * 128 + c0 + 32 * ch;
             float2 d2 = make_float2(0.f, 0.f);
             uint32_t dpk[16];
-            if (G.none) {
+            if (Gm.none) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) dpk[j] = 0u;
             } else {
@@ -938,8 +973,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float2 d = make_float2(keep_if_bit(__uint_as_float(rp2[2 * j]), G.vis, 2 * j),
-                                             keep_if_bit(__uint_as_float(rp2[2 * j + 1]), G.vis, 2 * j + 1));
+                const float2 d = make_float2(keep_if_bit(__uint_as_float(rp2[2 * j]), Gm.vis, 2 * j),
+                                             keep_if_bit(__uint_as_float(rp2[2 * j + 1]), Gm.vis, 2 * j + 1));
                 d2 = add2(d2, d);
                 dpk[j] = pack_bf16(d.x, d.y);
               }
@@ -951,8 +986,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           tc_fence_before_sync();
           warp_arrive(bars + B_DDONE + s, lane);
         }
-        // this tile's staging slot: piece 6 + 7 nt of the tile
-        rp.advance(6 + 7 * nt);
+        G += nt;
+        // this tile's staging slot: piece 6 + 6 nt of the tile
+        rp.advance(6 + 6 * nt);
         const uint32_t oslot = rp.slot;
         rp.advance();
         ph.wait(bars, B_OUTREADY, a.status, 183);
@@ -965,6 +1001,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         const float L = s_lz[row] + s_lz[128 + row];
         const float Zrow = s_lz[256 + row] + s_lz[384 + row];
         const float ZD = Zrow + (s_sd[row] + s_sd[128 + row]);
+        warp_arrive(bars + B_LZFREE, lane);
         // every thread has read the exchange before any output line is staged over it
         asm volatile("bar.sync 3, %0;" ::"n"(32 * WGRP) : "memory");
         ph.wait(bars, B_DONE, a.status, 182);
@@ -1001,8 +1038,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
                 make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
         }
         fence_async_smem();
-        // every thread of the group has staged its line (and read the row sums): one thread stores the tile,
-        // which clips rows past the end of the sequence, and releases the slot once the store has read it
+        // every thread of the group has staged its line: one thread stores the tile, which clips rows past the
+        // end of the sequence, and releases the slot once the store has read it
         asm volatile("bar.sync 3, %0;" ::"n"(32 * WGRP) : "memory");
         if (gtid == 0) {
           tma_store_4d(&a.tm_out, smem + OFF_RING + oslot * SLOT, 0, T.i0, T.h, T.b);
