@@ -15,21 +15,21 @@
 //             of a split are neighbours in the grid, so the K and V tiles they
 //             all read meet in L2.
 //   combine128  sums the split partials -> KV (fp32 and bf16), sum phi(K)
-//   band128   persistent, one CTA per SM walking a run of 128-query tiles.
-//             Tensor memory: O (128 columns) | two S/E/D buffers (2 x 128) | one
-//             feature HALF of phi(Q) (128 columns = 256 bf16 features).  The band
-//             is therefore walked twice per query tile:
-//               pass A (feature half 0): S = Q K^T, E = exp(tau S - pls), E -= P_0,
-//                      pack to bf16, O += D V;
-//               pass B (feature half 1): buffer = -P_1, pack, O += D V again
-//             (D = E - P_0 - P_1 is linear in its parts), with the low-rank
-//             product O += phi(Q)_h KV_h ahead of each pass.  Every B operand (K, V,
-//             phi(K), Wt and KV pieces) streams through ONE ring of 32 KB slots in
-//             exactly the order the single MMA-issuing warp consumes them; the
-//             finished output tile is staged in a slot of the same ring.  All MMAs
-//             are issued by one thread in program order, so buffer reuse between
-//             MMAs needs no barrier; barriers order the tensor core against the
-//             softmax warps only.
+//   band128   persistent, one CTA per SM, 128-query tiles dealt round-robin.
+//             Tensor memory: O (128 columns) | two S/E/D buffers (2 x 128) | feature
+//             half 0 of phi(Q) (128 columns = 256 bf16 features, formed in place
+//             over its U).  Half 1 does not fit: its U is parked in the second
+//             buffer at the start of a query tile and its features go to SHARED
+//             memory as a K-major operand, so the products over half 1 are SS-form
+//             MMAs.  Per key tile: S = Q K^T, E = exp(tau S - pls), E -= P_0 (A in
+//             tensor memory), E -= P_1 (A in shared memory), pack to bf16,
+//             O += D V; O += phi(Q)_h KV_h for both halves ahead of the key tiles.
+//             Every B operand (K, V, phi(K), Wt and KV pieces) streams through ONE
+//             ring of 32 KB slots in exactly the order the single MMA-issuing warp
+//             consumes them; the finished output tile is staged in a slot of the
+//             same ring.  All MMAs are issued by one thread in program order, so
+//             buffer reuse between MMAs needs no barrier; barriers order the tensor
+//             core against the softmax warps and the ring only.
 //
 // Feature order inside this path: slot kp = 128*q + 32*c + 16*s + j holds
 // feature exp((-1)^s u_p ...) of projection p = 64*q + 16*c + j (reference index
