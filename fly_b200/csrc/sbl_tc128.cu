@@ -126,8 +126,8 @@ struct Keys128Args {
 namespace keys128 {
 constexpr int TILE = 128;
 constexpr int NFEAT = 512;                 // feature threads: warp w owns key rows 32*(w%4).., 16 projections w/4
-constexpr int WPK = NFEAT / 32;            // producer warp; WPK+1: MMA warp
-constexpr int NTHREADS = NFEAT + 64;
+constexpr int WPK = NFEAT / 32;            // producer warp of W and K; WPK+1: MMA warp; WPK+2: producer warp of V
+constexpr int NTHREADS = NFEAT + 96;
 constexpr uint32_t OFF_W = 0;                     // 16 KB: two blocks [64 r][64 e] (e 0-63, e 64-127) of this quarter of Wt
 constexpr uint32_t OFF_K = 16384;                 // 2 x 32 KB: per key tile two blocks [128 keys][64 e]
 constexpr uint32_t OFF_V = OFF_K + 65536;         // 2 x 32 KB: per key tile two blocks [128 keys][64 d] (MN-major, N = 128)
@@ -224,6 +224,15 @@ __global__ void __launch_bounds__(keys128::NTHREADS) tc128_keys_kernel(const __g
         tma_load_4d(smem + OFF_K + s * 32768, &a.tm_k, k_full + s, 0, row0, h, b);
         tma_load_4d(smem + OFF_K + s * 32768 + 16384, &a.tm_k, k_full + s, 64, row0, h, b);
       }
+    }
+    __syncwarp();
+  } else if (warp == WPK + 2) {
+    // ---------------- producer of V: a warp of its own, so that the wait for a V slot (freed by the summary
+    // MMAs, late in a tile) does not hold back the next K tile, which the projection needs early ----------------
+    const bool leader = elect_one();
+    for (int i = 0; i < nt; ++i) {
+      const int s = i & 1;
+      const int row0 = (t_lo + i) * TILE;
       if (i >= 2) mbar_wait(v_empty + s, ((i >> 1) - 1) & 1, a.status, 112);
       if (leader) {
         mbar_expect_tx(v_full + s, 32768);
