@@ -1484,6 +1484,9 @@ __global__ void tc_fill_kernel(float* p, float v, int n) {
 bool tc_supported(const SblParams& p) {
   const bool shape64 = p.E == kE && p.D == kE && p.r == kR;
   if (p.dtype != SBL_DTYPE_BF16 || !(shape64 || tc128_shape(p))) return false;
+  // the d = 64 band kernel writes a query tile's MMA groups into a fixed list (one entry per key tile and a
+  // few more): windows that span more than 18 key tiles take the generic kernels
+  if (shape64 && p.w > 2048) return false;
   if (p.softmax_eps != 0.f) return false;
   const int64_t strides[] = {p.q_stride_b, p.q_stride_t, p.q_stride_h, p.k_stride_b, p.k_stride_s, p.k_stride_h,
                              p.v_stride_b, p.v_stride_s, p.v_stride_h, p.o_stride_b, p.o_stride_t, p.o_stride_h};

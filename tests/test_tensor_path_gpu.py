@@ -31,6 +31,24 @@ def _run(q, k, v, W, w, tau=None, lengths=None):
     return out.float().cpu()
 
 
+def test_very_wide_window_takes_the_generic_kernels(sbl_lib):
+    """d = 64 with a window of more than 2048 keys is outside the tensor-core band kernel's per-tile plan: the
+    problem must run the generic kernels (no status words) and still match the oracle."""
+    from fly_b200 import ops
+    q, k, v, W = _inputs(1, 3000, 3000, 1, seed=3)
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), 2500)
+    assert pr.status_offset is None
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 2500)
+    assert so.rel_err(pr.forward().float().cpu(), ref) <= TOL_BF16
+    # the widest window the tensor-core kernel takes
+    pr = ops.Problem(q.cuda(), k.cuda(), v.cuda(), W.cuda(), 2048)
+    assert pr.status_offset is not None
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 2048)
+    out = pr.forward().float().cpu()
+    pr.check_status()
+    assert so.rel_err(out, ref) <= TOL_BF16
+
+
 def test_library_reports_tensor_path(sbl_lib):
     assert sbl_lib.sbl_has_tensor_path() == 1
 
