@@ -365,3 +365,54 @@ def test_long_sequence_d128_sampled_rows(sbl_lib):
     for t0 in (0, 8000, N - 300):
         ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w, row_range=(t0, t0 + 300))
         assert so.rel_err(out[:, t0:t0 + 300], ref[:, t0:t0 + 300]) <= TOL_BF16
+
+
+def test_strided_views_and_clipped_output_d128(sbl_lib):
+    """d = 128: q, k, v as strided views of one packed projection (B, N, 3, H, E) and a caller-provided output that is
+    every other row of a larger buffer with T not a multiple of 128: exactly the T rows are written."""
+    from fly_b200 import ops
+    B, T, H, E, w = 1, 333, 2, 128, 512
+    g = torch.Generator().manual_seed(5)
+    qkv = (torch.randn(B, T, 3, H, E, generator=g) / E ** 0.25).bfloat16()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    torch.manual_seed(5)
+    W = so.gaussian_orthogonal_random_matrix(256, E)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, w)
+    qkv_d = qkv.cuda()
+    sentinel = 7.0
+    big = torch.full((B, 2 * T + 5, H, E), sentinel, dtype=torch.bfloat16, device='cuda')
+    out_view = big[:, 0:2 * T:2]
+    pr = ops.Problem(qkv_d[:, :, 0], qkv_d[:, :, 1], qkv_d[:, :, 2], W.cuda(), w, None, 0.0, None, out_view)
+    assert pr.status_offset is not None
+    out = pr.forward()
+    pr.check_status()
+    assert so.rel_err(out.float().cpu(), ref) <= TOL_BF16
+    untouched = torch.ones(2 * T + 5, dtype=torch.bool)
+    untouched[0:2 * T:2] = False
+    assert (big[:, untouched.cuda()] == sentinel).all()
+
+
+@pytest.mark.parametrize('tau', [0.3, 0.03])
+def test_temperatures_d128(tau, sbl_lib):
+    q, k, v, W = _inputs(1, 700, 700, 3, seed=5, E=128)
+    ref, _ = so.sblocal_forward(q.float(), k.float(), v.float(), W, 512, tau)
+    assert so.rel_err(_run(q, k, v, W, 512, tau), ref) <= TOL_BF16
+
+
+def test_bf16_compute_for_fp32_inputs_d128(sbl_lib):
+    """compute_dtype = bfloat16 on the module at the second tensor-core shape (d = 128, 512 features)."""
+    from fly_b200 import SBLocalAttention
+    torch.manual_seed(12)
+    B, N, H, E = 1, 900, 2, 128
+    q, k, v = [(torch.randn(B, N, H, E) / E ** 0.25) for _ in range(3)]
+    layer = SBLocalAttention(512, E, 512).cuda().eval()
+    with torch.no_grad():
+        out32, _ = layer(q.cuda(), k.cuda(), v.cuda())
+        W = layer.feature_map.projection_matrix.float().cpu()
+        ref, _ = so.sblocal_forward(q, k, v, W, 512)
+        assert so.rel_err(out32.cpu(), ref) <= 1e-4
+        layer.compute_dtype = torch.bfloat16
+        out16, _ = layer(q.cuda(), k.cuda(), v.cuda())
+    assert out16.dtype == torch.float32
+    assert so.rel_err(out16.cpu(), ref) <= TOL_BF16
+    assert not torch.equal(out16, out32)
