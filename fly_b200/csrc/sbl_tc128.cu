@@ -443,9 +443,11 @@ namespace band128 {
 constexpr int BQ = 128, KT = 128;
 constexpr int NSOFT = 512;                 // softmax threads: two groups of 256, warp w owns rows 32*(w%4)..
 constexpr int WGRP = 8;                    // warps per softmax group (exponential group, packing group)
-constexpr int W_LOAD = 16;                 // producer warp
-constexpr int W_MMA = 17;                  // MMA issuer warp
-constexpr int NTHREADS = NSOFT + 64;
+constexpr int W_LOAD = 16;                 // producer warp of the main ring (Wt, K, KV, V) and of Q
+constexpr int W_LOADP = 17;                // producer warp of the phi(K) ring
+constexpr int W_MMA = 18;                  // MMA issuer warp: U, S, low-rank, O
+constexpr int W_MMAP = 19;                 // MMA issuer warp: P
+constexpr int NTHREADS = NSOFT + 128;
 constexpr uint32_t OFF_Q = 0;              // 32 KB: two blocks [128 q][64 e]
 constexpr uint32_t OFF_PHI1 = 32768;       // 64 KB: feature half 1 of phi(Q), bf16, four blocks [128 q][64 f] (A operand)
 constexpr uint32_t OFF_RING = OFF_PHI1 + 65536;   // ring of 32 KB slots: every B operand, and the staged output tile
@@ -453,8 +455,9 @@ constexpr uint32_t OFF_RING = OFF_PHI1 + 65536;   // ring of 32 KB slots: every 
 // (L1), the row sums of D are exchanged through the output staging slot, and the kernel relies on (and checks) a
 // 1024-byte aligned shared-memory base.  (The ring is not deeper for a reason: what limits the operand stream is
 // the rate at which one SM takes data in, 32 KB per 785 cycles whatever the depth.)
-constexpr uint32_t NSLOT = 4, SLOT = 32768;
-constexpr uint32_t OFF_MISC = OFF_RING + NSLOT * SLOT;   // (L, Z) fp32[2][2][128]
+constexpr uint32_t NSLOT = 2, SLOT = 32768;       // slots of EACH of the two rings
+constexpr uint32_t OFF_RINGP = OFF_RING + NSLOT * SLOT;  // second ring: phi(K) pieces only, consumed by the P issuer
+constexpr uint32_t OFF_MISC = OFF_RINGP + NSLOT * SLOT;  // (L, Z) fp32[2][2][128]
 constexpr uint32_t OFF_BAR = OFF_MISC + 2048;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512;
 static_assert(SMEM_BYTES <= 232448, "dynamic shared memory of one CTA");
@@ -468,7 +471,10 @@ enum {
   B_QFREE,                        // Q buffer reusable: last MMA reading it + one arrival per exponential warp
   B_FULL,                         // [NSLOT] ring slot landed
   B_EMPTY = B_FULL + NSLOT,       // [NSLOT] ring slot consumed (MMAs done, or the output store has read it)
-  B_UFULL = B_EMPTY + NSLOT,      // [2] U half computed
+  B_PKFULL = B_EMPTY + NSLOT,     // [NSLOT] the same for the phi(K) ring
+  B_PKEMPTY = B_PKFULL + NSLOT,   // [NSLOT]
+  B_PFREE = B_PKEMPTY + NSLOT,    // every P product of the query tile done: both halves of phi(Q) may be replaced
+  B_UFULL,                        // [2] U half computed
   B_PHIFULL = B_UFULL + 2,        // [2] features of the half formed (one arrival per exponential warp)
   B_SFULL = B_PHIFULL + 2,        // [2] S computed into the buffer
   B_EDONE = B_SFULL + 2,          // [2] E written (one arrival per exponential warp)
@@ -527,11 +533,12 @@ struct RingPos {
   }
 };
 
-// Per query tile with nt key tiles, the ring carries 7 + 6 nt pieces in this order (the order of the issuer's
-// MMA groups):
+// Two rings of 32 KB slots, each with its own producer warp and its own MMA-issuing warp, so that the P products
+// (which wait for E and take four pieces each) and the rest do not hold each other up.  Per query tile with nt key
+// tiles the main ring carries 7 + 2 nt pieces in the order of its issuer's MMA groups:
 //   Wt half 0 | Wt half 1 | K(0) | KV half 0 (2) | K(1) | KV half 1 (2) |
-//   t = 0..nt:  phi(K)_0(t) (2), phi(K)_1(t) (2) [t < nt] | V(t-1) [t >= 1] | K(t+1) [1 <= t, t+1 < nt] |
-//   the output staging slot
+//   t = 1..nt:  V(t-1) | K(t+1) [t+1 < nt] |   the output staging slot
+// and the phi(K) ring 4 nt pieces:  t = 0..nt-1:  phi(K)_0(t) (2), phi(K)_1(t) (2).
 // Key tile t of a query tile uses buffer (G + t) & 1, G = key tiles of the earlier query tiles of this CTA.
 __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const __grid_constant__ Band128Args a) {
   using namespace band128;
@@ -626,17 +633,6 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         }
       }
     };
-    auto load_phik = [&](const Tile128& T, int half, int t) {   // two pieces of 128 features each
-      for (int j = 0; j < 2; ++j) {
-        const uint32_t s = acquire();
-        if (leader) {
-          uint8_t* dst = smem + OFF_RING + s * SLOT;
-          mbar_expect_tx(bars + B_FULL + s, 32768);
-          tma_load_3d(dst, &a.tm_phik, bars + B_FULL + s, 256 * half + 128 * j, T.j0 + t * KT, T.bh);
-          tma_load_3d(dst + 16384, &a.tm_phik, bars + B_FULL + s, 256 * half + 128 * j + 64, T.j0 + t * KT, T.bh);
-        }
-      }
-    };
     Tile128 T = tile128(a, 0), Tn{};
     load_q(T);
 #pragma unroll 1
@@ -667,13 +663,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       bool q_loaded = false;
 #pragma unroll 1
       for (int t = 0; t <= nt; ++t) {
-        if (t < nt) {
-          load_phik(T, 0, t);
-          load_phik(T, 1, t);
-        }
         if (have_next && !q_loaded && t >= nt - 1) {
-          // every S of this tile and both U halves have been issued by now (their pieces are at least four
-          // back in the ring): the Q buffer is about to be free
+          // every S of this tile and both U halves have been issued by now: the Q buffer is about to be free
           ph.wait(bars, B_QFREE, a.status, 151);
           load_q(Tn);
           q_loaded = true;
@@ -687,12 +678,81 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       __syncwarp();
       T = Tn;
     }
+  } else if (warp == W_LOADP) {
+    // ---------------- producer of the phi(K) ring ----------------
+    const bool leader = elect_one();
+    if (leader) prefetch_tmap(&a.tm_phik);
+    Phases ph;
+    RingPos rp;
+#pragma unroll 1
+    for (int it = 0; it < n_it; ++it) {
+      const Tile128 T = tile128(a, it);
+#pragma unroll 1
+      for (int t = 0; t < T.nt; ++t)
+#pragma unroll 1
+        for (int hj = 0; hj < 4; ++hj) {             // half hj / 2, piece hj % 2 of 128 features
+          const uint32_t s = rp.slot;
+          if (rp.wrapped) ph.wait(bars, B_PKEMPTY + s, a.status, 152);
+          rp.advance();
+          if (leader) {
+            uint8_t* dst = smem + OFF_RINGP + s * SLOT;
+            mbar_expect_tx(bars + B_PKFULL + s, 32768);
+            tma_load_3d(dst, &a.tm_phik, bars + B_PKFULL + s, 128 * hj, T.j0 + t * KT, T.bh);
+            tma_load_3d(dst + 16384, &a.tm_phik, bars + B_PKFULL + s, 128 * hj + 64, T.j0 + t * KT, T.bh);
+          }
+          __syncwarp();
+        }
+    }
+  } else if (warp == W_MMAP) {
+    // ---------------- MMA issuer of the P products: buffer -= phi(Q) phi(K)^T, half 0 (A in tensor memory), then
+    // half 1 (A in shared memory) ----------------
+    const bool leader = elect_one();
+    constexpr uint32_t id_neg = idesc_bf16(128, 128, false, false) | (1u << 13);   // bit 13 negates A
+    const uint64_t dPhi1 = smem_desc_sw128(smem_u32(smem + OFF_PHI1), 16, 1024);
+    const uint64_t dRingP = smem_desc_sw128(smem_u32(smem + OFF_RINGP), 16, 1024);
+    auto koff = [](int k) { return (uint64_t)((k >> 2) * (16384 >> 4) + (k & 3) * 2); };
+    Phases ph;
+    RingPos rp;
+    int G = 0;
+#pragma unroll 1
+    for (int it = 0; it < n_it; ++it) {
+      const int nt = tile128(a, it).nt;
+      ph.wait(bars, B_PHIFULL, a.status, 167);
+      ph.wait(bars, B_PHIFULL + 1, a.status, 168);
+#pragma unroll 1
+      for (int t = 0; t < nt; ++t) {
+        const int buf = (G + t) & 1;
+        ph.wait(bars, B_EDONE + buf, a.status, 165);
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t s = rp.slot;
+          ph.wait(bars, B_PKFULL + s, a.status, 169);
+          rp.advance();
+          tc_fence_after_sync();
+          if (leader) {
+            const uint64_t dB = dRingP + (uint64_t)(s * (SLOT >> 4));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if (j < 2)
+                mma_ts(tb + T_BUF + buf * 128, tb + T_PHI + 8 * (8 * j + k), dB + koff(k), id_neg, true);
+              else
+                mma_ss(tb + T_BUF + buf * 128, dPhi1 + koff(8 * (j - 2) + k), dB + koff(k), id_neg, true);
+            }
+            mma_commit(bars + B_PKEMPTY + s);
+            if (j == 3) mma_commit(bars + B_PDONE + buf);
+          }
+          __syncwarp();
+        }
+      }
+      if (leader) mma_commit(bars + B_PFREE);
+      __syncwarp();
+      G += nt;
+    }
   } else if (warp == W_MMA) {
-    // ---------------- MMA issuer: whole warp waits, one lane issues ----------------
+    // ---------------- main MMA issuer (U, S, low-rank, O): whole warp waits, one lane issues ----------------
     const bool leader = elect_one();
     constexpr uint32_t id_kk = idesc_bf16(128, 128, false, false);             // S, U: both operands K-major
     constexpr uint32_t id_mn = idesc_bf16(128, 128, false, true);              // low-rank, O: B = [K index][128 d]
-    constexpr uint32_t id_neg = idesc_bf16(128, 128, false, false) | (1u << 13);   // P: bit 13 negates A
     const uint64_t dQ = smem_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
     const uint64_t dPhi1 = smem_desc_sw128(smem_u32(smem + OFF_PHI1), 16, 1024);
     const uint64_t dRingK = smem_desc_sw128(smem_u32(smem + OFF_RING), 16, 1024);       // K-major piece
@@ -738,26 +798,6 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
         __syncwarp();
       }
     };
-    auto issue_p = [&](int buf) {   // buffer -= phi(Q) phi(K)^T: half 0 (A in tensor memory), then half 1 (A in shared memory)
-      ph.wait(bars, B_EDONE + buf, a.status, 165);
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t s = take();
-        tc_fence_after_sync();
-        if (leader) {
-          const uint64_t dB = dRingK + (uint64_t)(s * (SLOT >> 4));
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            if (j < 2)
-              mma_ts(tb + T_BUF + buf * 128, tb + T_PHI + 8 * (8 * j + k), dB + koff(k), id_neg, true);
-            else
-              mma_ss(tb + T_BUF + buf * 128, dPhi1 + koff(8 * (j - 2) + k), dB + koff(k), id_neg, true);
-          }
-          mma_commit(bars + B_EMPTY + s);
-          if (j == 3) mma_commit(bars + B_PDONE + buf);
-        }
-        __syncwarp();
-      }
-    };
     auto issue_o = [&](int buf) {   // O += D V: D packed bf16 sits in the first 16 of every 32 columns of the buffer
       ph.wait(bars, B_DDONE + buf, a.status, 162);
       const uint32_t s = take();
@@ -778,6 +818,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
       const int nt = tile128(a, it).nt;
       const int b0 = G & 1, b1 = b0 ^ 1;       // buffers of this tile's key tiles 0 and 1
       ph.wait(bars, B_QFULL, a.status, 163);
+      if (it >= 1) ph.wait(bars, B_PFREE, a.status, 174);       // the previous tile's P products are done with phi(Q)
       issue_qk(tb + T_PHI, bars + B_UFULL);                     // U half 0: features formed in place
       issue_qk(tb + T_BUF + b1 * 128, bars + B_UFULL + 1);      // U half 1: parked in the buffer of key tile 1
       if (nt > 0) issue_qk(tb + T_BUF + b0 * 128, bars + B_SFULL + b0);
@@ -797,7 +838,6 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
 #pragma unroll 1
       for (int t = 0; t <= nt; ++t) {
         const int buf = (G + t) & 1;
-        if (t < nt) issue_p(buf);
         if (t >= 1) issue_o(buf ^ 1);
         if (t >= 1 && t + 1 < nt) {
           issue_qk(tb + T_BUF + (buf ^ 1) * 128, bars + B_SFULL + (buf ^ 1));
@@ -996,8 +1036,8 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           warp_arrive(bars + B_DDONE + s, lane);
         }
         G += nt;
-        // this tile's staging slot: piece 6 + 6 nt of the tile
-        rp.advance(6 + 6 * nt);
+        // this tile's staging slot: piece 6 + 2 nt of the tile in the main ring
+        rp.advance(6 + 2 * nt);
         const uint32_t oslot = rp.slot;
         rp.advance();
         ph.wait(bars, B_OUTREADY, a.status, 183);
