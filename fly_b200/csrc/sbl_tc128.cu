@@ -536,8 +536,8 @@ struct RingPos {
 // Two rings of 32 KB slots, each with its own producer warp and its own MMA-issuing warp, so that the P products
 // (which wait for E and take four pieces each) and the rest do not hold each other up.  Per query tile with nt key
 // tiles the main ring carries 7 + 2 nt pieces in the order of its issuer's MMA groups:
-//   Wt half 0 | Wt half 1 | K(0) | KV half 0 (2) | K(1) | KV half 1 (2) |
-//   t = 1..nt:  V(t-1) | K(t+1) [t+1 < nt] |   the output staging slot
+//   Wt half 0 [first tile] | Wt half 1 | K(0) | KV half 0 (2) | K(1) | KV half 1 (2) |
+//   t = 1..nt:  Wt half 0 of the next tile [t = nt] | V(t-1) | K(t+1) [t+1 < nt] |   the output staging slot
 // and the phi(K) ring 4 nt pieces:  t = 0..nt-1:  phi(K)_0(t) (2), phi(K)_1(t) (2).
 // Key tile t of a query tile uses buffer (G + t) & 1, G = key tiles of the earlier query tiles of this CTA.
 __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const __grid_constant__ Band128Args a) {
@@ -654,7 +654,7 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           for (int x = 0; x < kM; x += 64) tma_prefetch_3d(&a.tm_phik, x, row0, Tn.bh);
         }
       }
-      load_w(0);
+      if (it == 0) load_w(0);     // later tiles: loaded at the tail of the tile before, see below
       load_w(1);
       if (nt > 0) load_rows(&a.tm_k, T, 0);
       load_kv(T, 0);
@@ -669,6 +669,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           load_q(Tn);
           q_loaded = true;
         }
+        // The first U half of the NEXT tile is computed ahead of this tile's last O += D V: the exponential warps,
+        // idle by then, turn it into features while this tile's packing and epilogue finish.
+        if (t == nt && have_next) load_w(0);
         if (t >= 1) load_rows(&a.tm_v, T, t - 1);
         if (t >= 1 && t + 1 < nt) load_rows(&a.tm_k, T, t + 1);
       }
@@ -817,9 +820,10 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
     for (int it = 0; it < n_it; ++it) {
       const int nt = tile128(a, it).nt;
       const int b0 = G & 1, b1 = b0 ^ 1;       // buffers of this tile's key tiles 0 and 1
-      ph.wait(bars, B_QFULL, a.status, 163);
-      if (it >= 1) ph.wait(bars, B_PFREE, a.status, 174);       // the previous tile's P products are done with phi(Q)
-      issue_qk(tb + T_PHI, bars + B_UFULL);                     // U half 0: features formed in place
+      if (it == 0) {
+        ph.wait(bars, B_QFULL, a.status, 163);
+        issue_qk(tb + T_PHI, bars + B_UFULL);                   // U half 0: features formed in place
+      }                                                         // (later tiles: issued at the tail of the tile before)
       issue_qk(tb + T_BUF + b1 * 128, bars + B_UFULL + 1);      // U half 1: parked in the buffer of key tile 1
       if (nt > 0) issue_qk(tb + T_BUF + b0 * 128, bars + B_SFULL + b0);
       if (it >= 1) ph.wait(bars, B_OFREE, a.status, 164);       // the previous tile's epilogue has read O
@@ -838,6 +842,13 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
 #pragma unroll 1
       for (int t = 0; t <= nt; ++t) {
         const int buf = (G + t) & 1;
+        if (t == nt && it + 1 < n_it) {
+          // U half 0 of the next tile, ahead of this tile's last O += D V: its Q tile has landed (every S of this
+          // tile has run), and this tile's P products are done with phi(Q)
+          ph.wait(bars, B_QFULL, a.status, 163);
+          ph.wait(bars, B_PFREE, a.status, 174);
+          issue_qk(tb + T_PHI, bars + B_UFULL);
+        }
         if (t >= 1) issue_o(buf ^ 1);
         if (t >= 1 && t + 1 < nt) {
           issue_qk(tb + T_BUF + (buf ^ 1) * 128, bars + B_SFULL + (buf ^ 1));
@@ -1036,8 +1047,9 @@ __global__ void __launch_bounds__(band128::NTHREADS, 1) tc128_band_kernel(const 
           warp_arrive(bars + B_DDONE + s, lane);
         }
         G += nt;
-        // this tile's staging slot: piece 6 + 2 nt of the tile in the main ring
-        rp.advance(6 + 2 * nt);
+        // this tile's staging slot in the main ring: behind Wt half 0 (first tile only), Wt half 1, nt K, 4 KV, nt V
+        // and the next tile's Wt half 0
+        rp.advance(5 + 2 * nt + (it == 0 ? 1 : 0) + (it + 1 < n_it ? 1 : 0));
         const uint32_t oslot = rp.slot;
         rp.advance();
         ph.wait(bars, B_OUTREADY, a.status, 183);
