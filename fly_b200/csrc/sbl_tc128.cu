@@ -24,12 +24,14 @@
 //             MMAs.  Per key tile: S = Q K^T, E = exp(tau S - pls), E -= P_0 (A in
 //             tensor memory), E -= P_1 (A in shared memory), pack to bf16,
 //             O += D V; O += phi(Q)_h KV_h for both halves ahead of the key tiles.
-//             Every B operand (K, V, phi(K), Wt and KV pieces) streams through ONE
-//             ring of 32 KB slots in exactly the order the single MMA-issuing warp
-//             consumes them; the finished output tile is staged in a slot of the
-//             same ring.  All MMAs are issued by one thread in program order, so
-//             buffer reuse between MMAs needs no barrier; barriers order the tensor
-//             core against the softmax warps and the ring only.
+//             Every B operand streams through a ring of 32 KB slots in exactly the
+//             order its MMA-issuing warp consumes it: the phi(K) pieces through
+//             one ring to the warp that issues the P products, K, V, Wt and KV
+//             pieces through another to the warp that issues everything else; the
+//             finished output tile is staged in a slot of the second ring.  Each
+//             issuer issues in program order, so buffer reuse between its own MMAs
+//             needs no barrier; barriers order the two issuers, the softmax warps
+//             and the rings.
 //
 // Feature order inside this path: slot kp = 128*q + 32*c + 16*s + j holds
 // feature exp((-1)^s u_p ...) of projection p = 64*q + 16*c + j (reference index
@@ -451,10 +453,10 @@ constexpr int NTHREADS = NSOFT + 128;
 constexpr uint32_t OFF_Q = 0;              // 32 KB: two blocks [128 q][64 e]
 constexpr uint32_t OFF_PHI1 = 32768;       // 64 KB: feature half 1 of phi(Q), bf16, four blocks [128 q][64 f] (A operand)
 constexpr uint32_t OFF_RING = OFF_PHI1 + 65536;   // ring of 32 KB slots: every B operand, and the staged output tile
-// Four slots, the Q tile and half of phi(Q) leave 2.5 KB of the 227 KB: the feature sums are read from global memory
-// (L1), the row sums of D are exchanged through the output staging slot, and the kernel relies on (and checks) a
-// 1024-byte aligned shared-memory base.  (The ring is not deeper for a reason: what limits the operand stream is
-// the rate at which one SM takes data in, 32 KB per 785 cycles whatever the depth.)
+// Four slots (two per ring), the Q tile and half of phi(Q) leave 2.5 KB of the 227 KB: the feature sums are read
+// from global memory (L1), the row sums of D are exchanged through the output staging slot, and the kernel relies
+// on (and checks) a 1024-byte aligned shared-memory base.  (The rings are not deeper for a reason: what limits the
+// operand stream is the rate at which one SM takes data in, 32 KB per 785 cycles whatever the depth.)
 constexpr uint32_t NSLOT = 2, SLOT = 32768;       // slots of EACH of the two rings
 constexpr uint32_t OFF_RINGP = OFF_RING + NSLOT * SLOT;  // second ring: phi(K) pieces only, consumed by the P issuer
 constexpr uint32_t OFF_MISC = OFF_RINGP + NSLOT * SLOT;  // (L, Z) fp32[2][2][128]
